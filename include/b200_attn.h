@@ -1,0 +1,116 @@
+/* b200_attn.h -- C ABI of the B200 (sm_100a) paged-KV attention library, libb200attn.so.
+ *
+ * The entry points are what a binding for nano-vllm's attention layer calls in place of the
+ * reference's Triton kernel and flash_attn calls.  File:line citations are relative to the
+ * nano-vllm project root.
+ *
+ * Conventions
+ *  - Every pointer is a device pointer on the current CUDA device unless stated otherwise.
+ *    The library never allocates, frees or copies device memory and never synchronises; every
+ *    launch goes to `stream` (a cudaStream_t passed as void*; NULL = legacy default stream), so
+ *    calls can be captured into CUDA graphs.
+ *  - Activations and caches are bf16 for the attention entry points.  head_dim must be 128.
+ *  - Strides are in ELEMENTS.  Pointers and row strides must be 16-byte aligned.
+ *  - The paged cache has the reference's layout (nanovllm/engine/model_runner.py:107-117): one
+ *    contiguous array (num_blocks, block_size, num_kv_heads, head_dim) for K and one for V;
+ *    flat slot = block_id * block_size + offset.  block_size must be a multiple of 256
+ *    (nanovllm/config.py:22).
+ *  - Block tables are int32 (batch, bt_cols) with row stride bt_row_stride; entries at columns
+ *    >= ceil(len / block_size) may hold -1 or stale ids (nanovllm/engine/model_runner.py:119-123,
+ *    :203) and are never dereferenced.
+ *  - Return value: 0 on success; negative = arguments rejected before any launch; positive = a
+ *    cudaError_t from the launch.  b200_last_error() describes the last failure of the calling
+ *    thread.  Nothing throws, aborts or traps.
+ */
+#ifndef B200_ATTN_H_
+#define B200_ATTN_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200_ATTN_VERSION 100
+
+#define B200_OK 0
+#define B200_ERR_NULL_POINTER (-1)
+#define B200_ERR_BAD_SHAPE (-2)
+#define B200_ERR_MISALIGNED (-3)
+#define B200_ERR_WORKSPACE (-4)
+#define B200_ERR_NO_DRIVER (-5)
+#define B200_ERR_TENSOR_MAP (-6)
+#define B200_ERR_DEVICE (-7)
+#define B200_ERR_TIMEOUT (-8)
+
+/* Library version (B200_ATTN_VERSION of the build). */
+int b200_version(void);
+
+/* Message for the last non-zero status returned to this thread ("" if none). Host pointer,
+ * valid until the thread's next failing call. */
+const char* b200_last_error(void);
+
+/* Replaces store_kvcache_kernel + store_kvcache (nanovllm/layers/attention.py:10-40).
+ * For token i in [0, n_tokens): slot = slot_mapping[i]; slot == -1 is skipped; otherwise the
+ * row_elems elements of key row i (at key + i * key_row_stride) are copied to flat cache row
+ * `slot` of k_cache, and likewise for value / v_cache.  Pure byte copy (any elem_bytes);
+ * row_elems * elem_bytes and both row strides must be multiples of 16 bytes.  Offsets are
+ * formed in 64 bits.  n_slots (= num_blocks * block_size) bounds the slot: an out-of-range
+ * slot is skipped, never written.  n_tokens == 0 is a no-op. */
+int b200_store_kvcache(const void* key, const void* value, int64_t key_row_stride, int64_t value_row_stride,
+                       void* k_cache, void* v_cache, const int32_t* slot_mapping, int32_t n_tokens,
+                       int32_t row_elems, int32_t elem_bytes, int64_t n_slots, void* stream);
+
+/* Bytes of workspace b200_decode_attn needs for any batch up to `max_batch` with this head
+ * geometry on the current device (depends on its multiprocessor count).  The caller allocates
+ * it once, ZERO-FILLS it once, and passes it to every call; the kernels leave the parts that
+ * must be zero as they found them.  Calls that share a workspace must not overlap on the GPU.
+ * Returns a negative status on bad arguments. */
+int64_t b200_decode_workspace_bytes(int32_t max_batch, int32_t num_heads, int32_t num_kv_heads, int32_t head_dim);
+
+/* Replaces flash_attn_with_kvcache as called for decode (nanovllm/layers/attention.py:71-74).
+ * For sequence i: the single query token q[i] (num_heads x head_dim at q + i * q_row_stride)
+ * attends the context_lens[i] cached tokens reached through block_tables[i, :]; GQA maps q head
+ * h to kv head h / (num_heads / num_kv_heads); softmax(scale * q k^T) v with fp32 softmax and
+ * accumulation; out[i] (num_heads x head_dim, contiguous rows of num_heads * head_dim) in bf16.
+ * context_lens[i] <= 0 writes zeros and touches no cache.  The launch geometry depends only on
+ * (batch, head geometry), never on device data. */
+int b200_decode_attn(const void* q, int64_t q_row_stride, const void* k_cache, const void* v_cache,
+                     int64_t num_blocks, int32_t block_size, const int32_t* block_tables, int64_t bt_row_stride,
+                     int32_t bt_cols, const int32_t* context_lens, void* out, void* workspace,
+                     int64_t workspace_bytes, int32_t batch, int32_t num_heads, int32_t num_kv_heads,
+                     int32_t head_dim, float scale, void* stream);
+
+/* Replaces flash_attn_varlen_func as called for prefill (nanovllm/layers/attention.py:64-70).
+ * Sequence i owns query rows cu_seqlens_q[i] .. cu_seqlens_q[i+1] of q (total_q, num_heads, 128)
+ * and keys 0 .. Lk_i - 1 with Lk_i = cu_seqlens_k[i+1] - cu_seqlens_k[i].  Causal mask aligned
+ * bottom-right: query row r sees keys 0 .. Lk_i - Lq_i + r.
+ *  - block_tables == NULL: dense K/V.  k, v are (total_k, num_kv_heads, 128) with row strides
+ *    k_row_stride / v_row_stride, sequence i's keys at rows cu_seqlens_k[i] ...
+ *  - block_tables != NULL (prefix cache): K/V for the whole key range come from k_cache/v_cache
+ *    through block_tables[i, t / block_size]; k and v are ignored.
+ * Sequences with Lq_i == 0 produce no rows.  out is (total_q, num_heads, 128) contiguous bf16.
+ * max_seqlen_q / max_seqlen_k are the host-side bounds the caller already has
+ * (nanovllm/utils/context.py:9-10).  kernel_variant: 0 = default, 1 = force the mma.sync
+ * kernel, 2 = force the tcgen05 kernel (returns B200_ERR_BAD_SHAPE if it cannot take the shape). */
+int b200_prefill_attn(const void* q, int64_t q_row_stride, const void* k, const void* v, int64_t k_row_stride,
+                      int64_t v_row_stride, int64_t total_k, const void* k_cache, const void* v_cache,
+                      int64_t num_blocks, int32_t block_size, const int32_t* block_tables, int64_t bt_row_stride,
+                      int32_t bt_cols, const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k, int32_t batch,
+                      int32_t total_q, int32_t max_seqlen_q, int32_t max_seqlen_k, void* out, int32_t num_heads,
+                      int32_t num_kv_heads, int32_t head_dim, float scale, int32_t kernel_variant, void* stream);
+
+/* Number of kernels this library has launched from the calling process so far (all threads).
+ * Benchmarks use the difference across a timed region. */
+int64_t b200_launch_count(void);
+
+/* Diagnostic, not for the hot path: synchronises the current device and returns
+ * B200_ERR_TIMEOUT if any kernel of this library gave up on a bounded wait since the library
+ * was loaded (its output is then undefined), a positive cudaError_t if the device reports an
+ * error, else 0. */
+int b200_device_status(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200_ATTN_H_ */

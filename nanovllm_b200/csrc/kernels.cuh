@@ -1,0 +1,31 @@
+// Declarations shared between the translation units of the library: prefill parameters and
+// launchers, and the per-unit device status words.
+#pragma once
+#include "common.cuh"
+
+namespace b200 {
+
+struct PrefillParams {
+  const __nv_bfloat16* q;
+  long long q_row_stride;
+  __nv_bfloat16* out;  // (total_q, H, 128) contiguous
+  const int* cu_q;
+  const int* cu_k;
+  const int* block_tables;  // nullptr: dense K/V
+  long long bt_row_stride;
+  int bt_cols;
+  int block_size;
+  long long num_blocks;
+  int batch, H, Hkv, G, QT;
+  int n_slots;  // upper bound on query tiles: total_q / QT + batch
+  int total_q, max_seqlen_q, max_seqlen_k;
+  float scale_log2;
+};
+
+int launch_prefill_mma(const PrefillParams& p, const CUtensorMap& map_k, const CUtensorMap& map_v, cudaStream_t stream);
+
+// Device-side "a bounded wait gave up" flags, one per translation unit, summed by b200_device_status().
+int read_status_decode();
+int read_status_prefill_mma();
+
+}  // namespace b200

@@ -1,0 +1,39 @@
+"""Installs the B200 attention layer into an importable nano-vllm, in place of
+nanovllm/layers/attention.py's `Attention` and `store_kvcache`.
+
+    import nanovllm_b200.integration as integ
+    integ.install()            # before constructing nanovllm.LLM
+    from nanovllm import LLM
+
+After install(), `nanovllm.models.qwen3.Qwen3Attention` builds this package's Attention
+(nanovllm/models/qwen3.py:60-65), the model runner binds the cache onto it
+(nanovllm/engine/model_runner.py:113-117) and the layer reads the engine's own per-step record
+(nanovllm/utils/context.py).  Tensor-parallel ranks are spawned processes that re-import
+everything; set B200_ATTN_INSTALL=1 in the environment and make `nanovllm_b200.autoinstall`
+importable at interpreter start (for instance through a `.pth` file or `sitecustomize`) to install
+there as well -- or start the ranks from a script that calls install() at import time.
+"""
+from __future__ import annotations
+
+import importlib
+import sys
+
+
+def install():
+    from .layers import attention as ours
+    ref_ctx = importlib.import_module("nanovllm.utils.context")
+    ours.set_context_getter(ref_ctx.get_context)
+    ref_attn = sys.modules.get("nanovllm.layers.attention")
+    if ref_attn is None:
+        # Register our module under the reference's name so that importing it never pulls in
+        # Triton or flash_attn.
+        sys.modules["nanovllm.layers.attention"] = ours
+        layers_pkg = importlib.import_module("nanovllm.layers")
+        setattr(layers_pkg, "attention", ours)
+    else:
+        ref_attn.Attention = ours.Attention
+        ref_attn.store_kvcache = ours.store_kvcache
+    qwen3 = sys.modules.get("nanovllm.models.qwen3")
+    if qwen3 is not None:
+        qwen3.Attention = ours.Attention
+    return ours

@@ -1,0 +1,418 @@
+"""GPU parity tests: the CUDA path (through the C ABI, via the layer that mirrors the reference's
+module) against the CPU oracle and the committed reference outputs.
+
+Tolerances are the ones BASELINE.json states: cache after store_kvcache bit-exact; attention
+outputs within 2e-2 abs + 1e-2 rel in bf16.
+"""
+import os
+
+import pytest
+import torch
+
+import cases
+from oracle.attention_oracle import (AttentionRef, Context, decode_attn_ref, decode_slots, default_scale,
+                                     make_block_tables, prefill_attn_ref, prefill_slots, store_kvcache_ref)
+
+pytestmark = pytest.mark.gpu
+
+ATOL, RTOL = 2e-2, 1e-2
+GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "golden.pt")
+DEV = "cuda:0"
+
+
+@pytest.fixture(scope="module")
+def b200():
+    import nanovllm_b200
+    from nanovllm_b200.utils import context as ctxmod
+    assert torch.cuda.is_available(), "GPU tests need a CUDA device"
+    return nanovllm_b200, ctxmod
+
+
+def _dev(x):
+    return None if x is None else x.to(DEV)
+
+
+def _set(ctxmod, ctx):
+    ctxmod.set_context(ctx.is_prefill, _dev(ctx.cu_seqlens_q), _dev(ctx.cu_seqlens_k), ctx.max_seqlen_q,
+                       ctx.max_seqlen_k, _dev(ctx.slot_mapping), _dev(ctx.context_lens), _dev(ctx.block_tables))
+
+
+def _close(a, b):
+    torch.testing.assert_close(a.float().cpu(), b.float().cpu(), atol=ATOL, rtol=RTOL)
+
+
+def _status_ok():
+    from nanovllm_b200 import _lib
+    _lib.check(_lib.load().b200_device_status())
+
+
+# ------------------------------------------------------------------------------------------------
+# golden cases: same seeded inputs as the reference run
+# ------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("name", list(cases.CASES))
+def test_golden_cases(b200, name):
+    pkg, ctxmod = b200
+    gold = torch.load(GOLD, weights_only=True)[name]
+    spec, t, ctx = cases.build_case(name)
+    same_inputs = cases.inputs_sha(t, ctx) == gold["inputs_sha"]
+    d = {k: v.to(DEV) for k, v in t.items()}
+    att = pkg.Attention(spec["H"], spec["D"], cases.scale_of(spec), spec["Hkv"])
+    if "k_cache" in d:
+        att.k_cache, att.v_cache = d["k_cache"], d["v_cache"]
+    _set(ctxmod, ctx)
+    out = att(d["q"], d["k"], d["v"])
+    torch.cuda.synchronize()
+    ctxmod.reset_context()
+    # oracle on the same inputs
+    ref = AttentionRef(spec["H"], spec["D"], cases.scale_of(spec), spec["Hkv"])
+    if "k_cache" in t:
+        ref.k_cache, ref.v_cache = t["k_cache"], t["v_cache"]
+    want = ref.forward(t["q"], t["k"], t["v"], ctx)
+    assert out.shape == want.shape and out.dtype == want.dtype
+    _close(out, want)
+    if "k_cache" in t:
+        assert torch.equal(d["k_cache"].cpu().view(torch.int16), t["k_cache"].view(torch.int16))
+        assert torch.equal(d["v_cache"].cpu().view(torch.int16), t["v_cache"].view(torch.int16))
+    if same_inputs:
+        _close(out, gold["out"])
+        if "k_cache" in t:
+            assert cases.tensor_sha(d["k_cache"]) == gold["k_cache_sha"]
+            assert cases.tensor_sha(d["v_cache"]) == gold["v_cache_sha"]
+    _status_ok()
+
+
+# ------------------------------------------------------------------------------------------------
+# store_kvcache: bit-exact byte copy
+# ------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32, torch.float16])
+@pytest.mark.parametrize("hkv,d,n", [(8, 128, 256), (1, 128, 7), (3, 64, 1000), (2, 128, 5000)])
+def test_store_bit_exact(b200, dtype, hkv, d, n):
+    pkg, _ = b200
+    g = torch.Generator().manual_seed(n * 31 + hkv)
+    nb, bs = 40, 256
+    k_cache = torch.randn(nb, bs, hkv, d, generator=g).to(dtype)
+    v_cache = torch.randn(nb, bs, hkv, d, generator=g).to(dtype)
+    fused = torch.randn(n, 4 * hkv * d, generator=g).to(dtype)
+    k = fused[:, hkv * d:2 * hkv * d].reshape(n, hkv, d).contiguous()
+    v = fused[:, 3 * hkv * d:].view(n, hkv, d)          # strided view, as the caller passes it
+    slots = torch.randperm(nb * bs, generator=g)[:n].to(torch.int32)
+    slots[::7] = -1                                        # padded graph rows
+    kc, vc = k_cache.to(DEV), v_cache.to(DEV)
+    fd = fused.to(DEV)
+    kd = k.to(DEV)
+    vd = fd[:, 3 * hkv * d:].view(n, hkv, d)
+    assert vd.stride(0) == 4 * hkv * d
+    pkg.store_kvcache(kd, vd, kc, vc, slots.to(DEV))
+    torch.cuda.synchronize()
+    store_kvcache_ref(k, v, k_cache, v_cache, slots)
+    view = {torch.bfloat16: torch.int16, torch.float16: torch.int16, torch.float32: torch.int32}[dtype]
+    assert torch.equal(kc.cpu().view(view), k_cache.view(view))
+    assert torch.equal(vc.cpu().view(view), v_cache.view(view))
+
+
+def test_store_empty_and_all_skipped(b200):
+    pkg, _ = b200
+    kc = torch.zeros(2, 256, 2, 128, dtype=torch.bfloat16, device=DEV)
+    vc = torch.zeros_like(kc)
+    k = torch.ones(0, 2, 128, dtype=torch.bfloat16, device=DEV)
+    pkg.store_kvcache(k, k, kc, vc, torch.zeros(0, dtype=torch.int32, device=DEV))
+    k = torch.ones(5, 2, 128, dtype=torch.bfloat16, device=DEV)
+    pkg.store_kvcache(k, k, kc, vc, torch.full((5,), -1, dtype=torch.int32, device=DEV))
+    torch.cuda.synchronize()
+    assert not kc.any() and not vc.any()
+
+
+# ------------------------------------------------------------------------------------------------
+# decode
+# ------------------------------------------------------------------------------------------------
+def _decode_case(seed, lens, h, hkv, nb=None, poison=True, bt_extra_cols=0, scale_in=0.5):
+    g = torch.Generator().manual_seed(seed)
+    d, bs = 128, 256
+    bt, nb = make_block_tables(lens, bs, g, num_blocks=nb)
+    k_cache = (torch.randn(nb, bs, hkv, d, generator=g) * scale_in).to(torch.bfloat16)
+    v_cache = (torch.randn(nb, bs, hkv, d, generator=g) * scale_in).to(torch.bfloat16)
+    if poison:
+        # every slot no sequence owns holds NaN: reading one shows up in the output
+        owned = torch.zeros(nb * bs, dtype=torch.bool)
+        for i, n in enumerate(lens):
+            for t0 in range(0, n, bs):
+                b = int(bt[i, t0 // bs])
+                owned[b * bs: b * bs + min(bs, n - t0)] = True
+        k_cache.view(-1, hkv, d)[~owned] = float("nan")
+        v_cache.view(-1, hkv, d)[~owned] = float("nan")
+    if bt_extra_cols:
+        # stale tails: columns past ceil(len / block) hold ids that must never be dereferenced
+        junk = torch.randint(-5, 1 << 30, (len(lens), bt_extra_cols), generator=g, dtype=torch.int32)
+        wide = torch.cat([bt, junk], dim=1)
+        for i, n in enumerate(lens):
+            used = (n + bs - 1) // bs
+            wide[i, used:bt.shape[1]] = junk[i, 0]
+        bt = wide
+    q = (torch.randn(len(lens), h, d, generator=g) * scale_in).to(torch.bfloat16)
+    return q, k_cache, v_cache, torch.tensor(lens, dtype=torch.int32), bt
+
+
+def _run_decode(pkg, q, kc, vc, lens, bt, hkv):
+    out = pkg.decode_attention(q.to(DEV), kc.to(DEV), vc.to(DEV), lens.to(DEV), bt.to(DEV),
+                               default_scale(128), hkv)
+    torch.cuda.synchronize()
+    return out
+
+
+@pytest.mark.parametrize("h,hkv", [(16, 8), (4, 1), (2, 1), (8, 8), (32, 8), (16, 1), (5, 1)])
+def test_decode_ragged_poisoned(b200, h, hkv):
+    pkg, _ = b200
+    lens = [1, 63, 64, 65, 0, 255, 256, 257, 1000, 16, 15, 17, 4096, 0, 777]
+    q, kc, vc, cl, bt = _decode_case(7 + h, lens, h, hkv, bt_extra_cols=3)
+    out = _run_decode(pkg, q, kc, vc, cl, bt, hkv)
+    want = decode_attn_ref(q, kc, vc, cl, bt, default_scale(128))
+    assert torch.isfinite(out.float()).all()
+    _close(out, want)
+    assert not out[4].any() and not out[13].any()          # zero-length rows are zeros
+    _status_ok()
+
+
+def test_decode_single_long_sequence_split_over_many_ctas(b200):
+    pkg, _ = b200
+    for lens in ([8192], [8191, 3], [70000]):
+        q, kc, vc, cl, bt = _decode_case(11, lens, 4, 1, poison=False)
+        out = _run_decode(pkg, q, kc, vc, cl, bt, 1)
+        _close(out, decode_attn_ref(q, kc, vc, cl, bt, default_scale(128)))
+    _status_ok()
+
+
+def test_decode_large_batch_eager_path(b200):
+    pkg, _ = b200
+    g = torch.Generator().manual_seed(5)
+    lens = torch.randint(1, 300, (1100,), generator=g).tolist()   # > 1024: split across launches
+    q, kc, vc, cl, bt = _decode_case(12, lens, 4, 2, poison=False)
+    out = _run_decode(pkg, q, kc, vc, cl, bt, 2)
+    _close(out, decode_attn_ref(q, kc, vc, cl, bt, default_scale(128)))
+
+
+def test_decode_config2_shape_repeatable(b200):
+    """BASELINE config 2 at full size; oracle on a sample of rows; two runs bit-identical."""
+    pkg, _ = b200
+    g = torch.Generator().manual_seed(2)
+    lens = torch.randint(100, 2049, (256,), generator=g).tolist()
+    q, kc, vc, cl, bt = _decode_case(13, lens, 16, 8, poison=False)
+    qd, kd, vd, cd, bd = (x.to(DEV) for x in (q, kc, vc, cl, bt))
+    o1 = pkg.decode_attention(qd, kd, vd, cd, bd, default_scale(128), 8)
+    o2 = pkg.decode_attention(qd, kd, vd, cd, bd, default_scale(128), 8)
+    torch.cuda.synchronize()
+    rows = list(range(0, 256, 16))
+    want = decode_attn_ref(q[rows], kc, vc, cl[rows], bt[rows], default_scale(128))
+    _close(o1[rows], want)
+    # the split points do not depend on timing, but the merge order of partials does not either
+    _close(o1, o2)
+    _status_ok()
+
+
+def test_decode_cuda_graph_capture_replay(b200):
+    """Capture with all-zero metadata in static buffers (nanovllm/engine/model_runner.py:215-250),
+    replay with real metadata and padded rows (slot -1, len 0, stale table rows)."""
+    pkg, ctxmod = b200
+    h, hkv, d, bs_bucket, cols = 16, 8, 128, 16, 16
+    lens = [300, 1, 4096, 513, 77]
+    q, kc, vc, cl, bt = _decode_case(21, lens, h, hkv, nb=40, poison=False)
+    g = torch.Generator().manual_seed(22)
+    knew = (torch.randn(len(lens), hkv, d, generator=g) * 0.5).to(torch.bfloat16)
+    vnew = (torch.randn(len(lens), hkv, d, generator=g) * 0.5).to(torch.bfloat16)
+    slots = decode_slots(lens, bt, 256)
+    att = pkg.Attention(h, d, default_scale(d), hkv)
+    att.k_cache, att.v_cache = kc.to(DEV), vc.to(DEV)
+    s_q = torch.zeros(bs_bucket, h, d, dtype=torch.bfloat16, device=DEV)
+    s_k = torch.zeros(bs_bucket, hkv, d, dtype=torch.bfloat16, device=DEV)
+    s_v = torch.zeros(bs_bucket, hkv, d, dtype=torch.bfloat16, device=DEV)
+    s_slot = torch.zeros(bs_bucket, dtype=torch.int32, device=DEV)
+    s_len = torch.zeros(bs_bucket, dtype=torch.int32, device=DEV)
+    s_bt = torch.zeros(bs_bucket, cols, dtype=torch.int32, device=DEV)
+    s_out = torch.zeros(bs_bucket, 1, h, d, dtype=torch.bfloat16, device=DEV)
+    slot0_before = (att.k_cache.view(-1, hkv * d)[0].clone(), att.v_cache.view(-1, hkv * d)[0].clone())
+    ctxmod.set_context(False, slot_mapping=s_slot, context_lens=s_len, block_tables=s_bt)
+    with torch.inference_mode():
+        s_out.copy_(att(s_q, s_k, s_v))            # warm-up, as the reference does
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            s_out.copy_(att(s_q, s_k, s_v))
+    torch.cuda.synchronize()
+    # capture wrote the zero rows to slot 0; put the original back so the oracle sees the same cache
+    att.k_cache.view(-1, hkv * d)[0] = slot0_before[0]
+    att.v_cache.view(-1, hkv * d)[0] = slot0_before[1]
+    n = len(lens)
+    s_q[:n] = q.to(DEV); s_k[:n] = knew.to(DEV); s_v[:n] = vnew.to(DEV)
+    s_slot.fill_(-1); s_slot[:n] = slots.to(DEV)
+    s_len.zero_(); s_len[:n] = cl.to(DEV)
+    s_bt.fill_(12345678)                           # stale ids everywhere ...
+    s_bt[:n, :bt.shape[1]] = bt.to(DEV)            # ... except what the step wrote
+    graph.replay()
+    torch.cuda.synchronize()
+    ctxmod.reset_context()
+    store_kvcache_ref(knew, vnew, kc, vc, slots)
+    want = decode_attn_ref(q, kc, vc, cl, bt.clamp_min(0), default_scale(d))
+    _close(s_out[:n], want)
+    assert not s_out[n:].any()
+    assert torch.equal(att.k_cache.cpu().view(torch.int16), kc.view(torch.int16))
+    _status_ok()
+
+
+# ------------------------------------------------------------------------------------------------
+# prefill
+# ------------------------------------------------------------------------------------------------
+def _prefill_case(seed, lens, prefix, h, hkv, paged, poison=True):
+    g = torch.Generator().manual_seed(seed)
+    d, bs = 128, 256
+    lq = [a - b for a, b in zip(lens, prefix)]
+    cu_q = torch.tensor([0] + lq).cumsum(0).to(torch.int32)
+    cu_k = torch.tensor([0] + lens).cumsum(0).to(torch.int32)
+    q = torch.randn(int(cu_q[-1]), h, d, generator=g).to(torch.bfloat16)
+    if not paged:
+        fused = torch.randn(int(cu_k[-1]), 2 * hkv * d, generator=g).to(torch.bfloat16)
+        k = fused[:, :hkv * d].reshape(-1, hkv, d).contiguous()
+        v = fused[:, hkv * d:].view(-1, hkv, d)
+        return q, k, v, cu_q, cu_k, None, fused
+    bt, nb = make_block_tables(lens, bs, g)
+    kc = torch.randn(nb, bs, hkv, d, generator=g).to(torch.bfloat16)
+    vc = torch.randn(nb, bs, hkv, d, generator=g).to(torch.bfloat16)
+    if poison:
+        owned = torch.zeros(nb * bs, dtype=torch.bool)
+        for i, n in enumerate(lens):
+            for t0 in range(0, n, bs):
+                b = int(bt[i, t0 // bs])
+                owned[b * bs: b * bs + min(bs, n - t0)] = True
+        kc.view(-1, hkv, d)[~owned] = float("nan")
+        vc.view(-1, hkv, d)[~owned] = float("nan")
+    return q, kc, vc, cu_q, cu_k, bt, None
+
+
+@pytest.mark.parametrize("h,hkv", [(16, 8), (4, 1), (2, 2), (5, 1), (8, 1)])
+def test_prefill_dense_ragged(b200, h, hkv):
+    pkg, _ = b200
+    lens = [1, 2, 63, 64, 65, 127, 128, 129, 500, 1024, 31]
+    q, k, v, cu_q, cu_k, _, fused = _prefill_case(31 + h, lens, [0] * len(lens), h, hkv, paged=False)
+    fd = fused.to(DEV)
+    kd = k.to(DEV)
+    vd = fd[:, hkv * 128:].view(-1, hkv, 128)
+    out = pkg.prefill_attention(q.to(DEV), kd, vd, cu_q.to(DEV), cu_k.to(DEV), max(lens), max(lens),
+                                default_scale(128), hkv)
+    torch.cuda.synchronize()
+    want = prefill_attn_ref(q, k, v, cu_q, cu_k, default_scale(128))
+    assert torch.isfinite(out.float()).all()
+    _close(out, want)
+    _status_ok()
+
+
+@pytest.mark.parametrize("h,hkv", [(16, 8), (4, 1), (2, 2)])
+def test_prefill_paged_prefix_poisoned(b200, h, hkv):
+    pkg, _ = b200
+    lens = [300, 600, 513, 256, 700, 1025, 512, 40]
+    prefix = [0, 256, 512, 0, 512, 768, 512, 0]          # one sequence fully cached: no query rows
+    q, kc, vc, cu_q, cu_k, bt, _ = _prefill_case(41 + h, lens, prefix, h, hkv, paged=True)
+    lq = [a - b for a, b in zip(lens, prefix)]
+    out = pkg.prefill_attention(q.to(DEV), kc.to(DEV), vc.to(DEV), cu_q.to(DEV), cu_k.to(DEV), max(lq), max(lens),
+                                default_scale(128), hkv, block_tables=bt.to(DEV))
+    torch.cuda.synchronize()
+    want = prefill_attn_ref(q, kc, vc, cu_q, cu_k, default_scale(128), bt)
+    assert torch.isfinite(out.float()).all()
+    _close(out, want)
+    _status_ok()
+
+
+def test_prefill_module_store_then_attend(b200):
+    """The layer's prefill path with a bound cache: new K/V are stored first, then read back
+    through the block tables together with the cached prefix."""
+    pkg, ctxmod = b200
+    h, hkv, d = 16, 8, 128
+    lens, prefix = [700, 300, 520], [512, 0, 256]
+    g = torch.Generator().manual_seed(51)
+    bt, nb = make_block_tables(lens, 256, g)
+    kc = torch.randn(nb, 256, hkv, d, generator=g).to(torch.bfloat16)
+    vc = torch.randn(nb, 256, hkv, d, generator=g).to(torch.bfloat16)
+    lq = [a - b for a, b in zip(lens, prefix)]
+    n = sum(lq)
+    q = torch.randn(n, h, d, generator=g).to(torch.bfloat16)
+    k = torch.randn(n, hkv, d, generator=g).to(torch.bfloat16)
+    v = torch.randn(n, hkv, d, generator=g).to(torch.bfloat16)
+    ctx = Context(True, torch.tensor([0] + lq).cumsum(0).to(torch.int32), torch.tensor([0] + lens).cumsum(0).to(torch.int32),
+                  max(lq), max(lens), prefill_slots(lens, prefix, bt, 256), None, bt)
+    att = pkg.Attention(h, d, default_scale(d), hkv)
+    att.k_cache, att.v_cache = kc.to(DEV), vc.to(DEV)
+    _set(ctxmod, ctx)
+    out = att(q.to(DEV), k.to(DEV), v.to(DEV))
+    torch.cuda.synchronize()
+    ctxmod.reset_context()
+    ref = AttentionRef(h, d, default_scale(d), hkv)
+    ref.k_cache, ref.v_cache = kc, vc
+    want = ref.forward(q, k, v, ctx)
+    _close(out, want)
+    assert torch.equal(att.k_cache.cpu().view(torch.int16), kc.view(torch.int16))
+    assert torch.equal(att.v_cache.cpu().view(torch.int16), vc.view(torch.int16))
+
+
+def test_prefill_warmup_shape_no_cache(b200):
+    """The engine's warm-up: 4 x 4096 tokens, no cache bound, empty slot_mapping
+    (nanovllm/engine/model_runner.py:91-98)."""
+    pkg, ctxmod = b200
+    h, hkv, d = 16, 8, 128
+    lens = [4096] * 2
+    g = torch.Generator().manual_seed(61)
+    q = torch.randn(sum(lens), h, d, generator=g).to(torch.bfloat16)
+    k = torch.randn(sum(lens), hkv, d, generator=g).to(torch.bfloat16)
+    v = torch.randn(sum(lens), hkv, d, generator=g).to(torch.bfloat16)
+    cu = torch.tensor([0] + lens).cumsum(0).to(torch.int32)
+    att = pkg.Attention(h, d, default_scale(d), hkv)
+    ctxmod.set_context(True, cu.to(DEV), cu.to(DEV), 4096, 4096, torch.zeros(0, dtype=torch.int32, device=DEV), None, None)
+    out = att(q.to(DEV), k.to(DEV), v.to(DEV))
+    torch.cuda.synchronize()
+    ctxmod.reset_context()
+    rows = torch.cat([torch.arange(0, 4096, 97), torch.arange(4096 + 4000, 8192, 13)])
+    want = prefill_attn_ref(q, k, v, cu, cu, default_scale(d))
+    _close(out[rows], want[rows])
+
+
+# ------------------------------------------------------------------------------------------------
+# against the reference's attention library, live, when it is importable on the box
+# ------------------------------------------------------------------------------------------------
+def test_live_against_flash_attn(b200):
+    pkg, _ = b200
+    fa = pytest.importorskip("flash_attn")
+    g = torch.Generator().manual_seed(71)
+    lens = torch.randint(100, 2049, (64,), generator=g).tolist()
+    q, kc, vc, cl, bt = _decode_case(72, lens, 16, 8, poison=False)
+    qd, kd, vd, cd, bd = (x.to(DEV) for x in (q, kc, vc, cl, bt))
+    ours = pkg.decode_attention(qd, kd, vd, cd, bd, default_scale(128), 8)
+    theirs = fa.flash_attn_with_kvcache(qd.unsqueeze(1), kd, vd, cache_seqlens=cd, block_table=bd,
+                                        softmax_scale=default_scale(128), causal=True)
+    _close(ours, theirs)
+    lens = torch.randint(100, 1025, (24,), generator=g).tolist()
+    qp, k, v, cu_q, cu_k, _, _ = _prefill_case(73, lens, [0] * len(lens), 16, 8, paged=False)
+    ours = pkg.prefill_attention(qp.to(DEV), k.to(DEV), v.to(DEV).contiguous(), cu_q.to(DEV), cu_k.to(DEV), max(lens),
+                                 max(lens), default_scale(128), 8)
+    theirs = fa.flash_attn_varlen_func(qp.to(DEV), k.to(DEV), v.to(DEV).contiguous(), cu_seqlens_q=cu_q.to(DEV),
+                                       cu_seqlens_k=cu_k.to(DEV), max_seqlen_q=max(lens), max_seqlen_k=max(lens),
+                                       softmax_scale=default_scale(128), causal=True)
+    _close(ours, theirs)
+
+
+# ------------------------------------------------------------------------------------------------
+# argument checking through the C ABI
+# ------------------------------------------------------------------------------------------------
+def test_error_codes(b200):
+    from nanovllm_b200 import _lib
+    lib = _lib.load()
+    x = torch.zeros(4096, dtype=torch.uint8, device=DEV)
+    p = x.data_ptr()
+    assert lib.b200_store_kvcache(None, p, 128, 128, p, p, p, 1, 128, 2, 1, None) == -1
+    assert lib.b200_store_kvcache(p, p, 128, 128, p, p, p, 1, 100, 2, 1, None) == -3
+    assert lib.b200_store_kvcache(p + 2, p, 128, 128, p, p, p, 1, 128, 2, 1, None) == -3
+    assert lib.b200_decode_attn(p, 2048, p, p, 1, 256, p, 1, 1, p, p, p, 4096, 1, 16, 8, 64, 0.1, None) == -2
+    assert lib.b200_decode_attn(p, 2048, p, p, 1, 128, p, 1, 1, p, p, p, 4096, 1, 16, 8, 128, 0.1, None) == -2
+    assert lib.b200_decode_attn(p, 2048, p, p, 1, 256, p, 1, 1, p, p, p, 4096, 1, 16, 8, 128, 0.1, None) == -4
+    assert lib.b200_decode_attn(p, 2048, p, p, 1, 256, p, 1, 1, p, p, None, 0, 1, 16, 7, 128, 0.1, None) == -2
+    assert b"workspace" in lib.b200_last_error() or b"num_heads" in lib.b200_last_error()
+    assert lib.b200_prefill_attn(p, 2048, None, None, 0, 0, 0, None, None, 0, 0, None, 0, 0, p, p, 1, 4, 4, 4, p,
+                                 16, 8, 128, 0.1, 0, None) == -1
+    with pytest.raises(RuntimeError):
+        pkg = b200[0]
+        pkg.decode_attention(torch.zeros(1, 16, 128, dtype=torch.bfloat16), x, x, x, x, 0.1, 8)   # CPU tensor
+    _status_ok()
