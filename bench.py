@@ -1,0 +1,399 @@
+#!/usr/bin/env python
+"""Benchmark of the paged-KV attention path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+Prints ONE JSON line.  Default workload `decode_cfg2` is the configuration the headline metric
+(paged decode-attention HBM GB/s) is quoted on: Qwen3-0.6B attention geometry (16 q heads, 8 kv
+heads, head_dim 128), batch 256, context lengths uniform in [100, 2048], block size 256,
+scattered random block tables, bf16.  One step = store_kvcache of one new token per sequence
+followed by paged decode attention, on one layer's cache; consecutive steps walk over several
+layers' caches (several GB in total), so no step finds its K/V in L2.
+
+With N > 1 the path is sharded exactly as the reference's tensor parallelism does it -- by KV
+head, identical metadata on every rank, no collective in the data path -- and `value` is the
+bytes all ranks processed divided by the slowest rank's device time ("strong" scaling: the
+global problem is fixed).  `--workload decode_cfg4` runs the Qwen3-8B geometry (32/8 heads,
+batch 512, lengths in [512, 8192]) the same way; `--workload prefill_cfg3` reports prefill
+attention TFLOP/s instead.
+
+`--impl reference` times the reference's algorithm on the host cores (the CPU restatement under
+oracle/, torch with all host threads) on a bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    "decode_cfg2": dict(kind="decode", H=16, Hkv=8, D=128, batch=256, lo=100, hi=2048, seed=2, layers=8),
+    "decode_cfg4": dict(kind="decode", H=32, Hkv=8, D=128, batch=512, lo=512, hi=8192, seed=4, layers=3),
+    "prefill_cfg3": dict(kind="prefill", H=16, Hkv=8, D=128, batch=256, lo=100, hi=1024, seed=3),
+}
+BLOCK = 256
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return dict(hbm=float(p["hbm_gbs"]), bf16=float(p["bf16_tflops"]), source="measured")
+    return dict(hbm=6650.0, bf16=1590.0, source="fallback")
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons sampled while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.idx = gpu_index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            f = tempfile.NamedTemporaryFile("w", suffix=".csv", delete=False)
+            self.path = f.name
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.idx), "--query-gpu=" + self.Q,
+                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=f,
+                                         stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        rows = []
+        try:
+            for line in open(self.path):
+                c = [x.strip() for x in line.split(",")]
+                if len(c) >= 9:
+                    rows.append(c)
+            os.unlink(self.path)
+        except Exception:
+            pass
+        if not rows:
+            return out
+        sm = [float(r[1]) for r in rows if r[1].replace(".", "").isdigit()]
+        mx = [float(r[2]) for r in rows if r[2].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for j, n in enumerate(names) if any(r[5 + j].lower().startswith("active") for r in rows)]
+        # "under load": the upper half of the samples (idle samples before/after the region read low)
+        load = sorted(sm)[len(sm) // 2:] if sm else []
+        out.update(sm_mhz=statistics.median(load) if load else None, sm_max_mhz=max(mx) if mx else None,
+                   reasons=reasons, samples=len(rows))
+        return out
+
+
+def dist_env():
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    return rank, world, local
+
+
+def seeded_lens(w):
+    g = torch.Generator().manual_seed(w["seed"])
+    return torch.randint(w["lo"], w["hi"] + 1, (w["batch"],), generator=g, dtype=torch.int32), g
+
+
+# --------------------------------------------------------------------------------------------
+# decode workload (ours)
+# --------------------------------------------------------------------------------------------
+def run_decode(args, w, rank, world, local):
+    import torch.distributed as dist
+    import nanovllm_b200
+    from nanovllm_b200 import _lib
+    from nanovllm_b200.sharding import local_heads
+    from nanovllm_b200.utils.context import reset_context, set_context
+    from oracle.attention_oracle import decode_algorithmic_bytes, decode_slots, make_block_tables
+
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    lib = _lib.load()
+    h, hkv = local_heads(w["H"], w["Hkv"], world)
+    d, b = w["D"], w["batch"]
+    scale = d ** -0.5
+    lens, g = seeded_lens(w)                      # identical metadata on every rank
+    bt, nb = make_block_tables(lens.tolist(), BLOCK, g)
+    slots = decode_slots(lens.tolist(), bt, BLOCK)
+    layers = args.layers or w["layers"]
+    gd = torch.Generator(device=dev).manual_seed(1000 + rank)
+    caches = []
+    for _ in range(layers):
+        kc = torch.randn(nb, BLOCK, hkv, d, device=dev, dtype=torch.bfloat16, generator=gd) * 0.5
+        vc = torch.randn(nb, BLOCK, hkv, d, device=dev, dtype=torch.bfloat16, generator=gd) * 0.5
+        caches.append((kc, vc))
+    att = nanovllm_b200.Attention(h, d, scale, hkv)
+    # host-side step inputs (pinned), as the model runner prepares them
+    hq = (torch.randn(b, h, d, generator=g) * 0.5).to(torch.bfloat16).pin_memory()
+    hk = (torch.randn(b, hkv, d, generator=g) * 0.5).to(torch.bfloat16).pin_memory()
+    hv = (torch.randn(b, hkv, d, generator=g) * 0.5).to(torch.bfloat16).pin_memory()
+    h_slots, h_lens, h_bt = slots.pin_memory(), lens.pin_memory(), bt.pin_memory()
+    dq, dk, dv = hq.to(dev), hk.to(dev), hv.to(dev)
+    d_slots, d_lens, d_bt = h_slots.to(dev), h_lens.to(dev), h_bt.to(dev)
+    h_out = torch.empty(b, 1, h, d, dtype=torch.bfloat16).pin_memory()
+
+    dec_bytes = decode_algorithmic_bytes(lens, h, hkv, d)
+    store_bytes = 2 * (2 * b * hkv * d * 2) + 4 * b          # K and V rows read + written, slots read
+    step_bytes = dec_bytes + store_bytes
+
+    def step_resident(i, ev=None):
+        kc, vc = caches[i % layers]
+        nanovllm_b200.store_kvcache(dk, dv, kc, vc, d_slots)
+        if ev is not None:
+            ev[0].record()
+        o = nanovllm_b200.decode_attention(dq, kc, vc, d_lens, d_bt, scale, hkv)
+        if ev is not None:
+            ev[1].record()
+        return o
+
+    def step_e2e(i):
+        att.k_cache, att.v_cache = caches[i % layers]
+        q_, k_, v_ = hq.to(dev, non_blocking=True), hk.to(dev, non_blocking=True), hv.to(dev, non_blocking=True)
+        set_context(False, slot_mapping=h_slots.to(dev, non_blocking=True),
+                    context_lens=h_lens.to(dev, non_blocking=True), block_tables=h_bt.to(dev, non_blocking=True))
+        o = att(q_, k_, v_)
+        h_out.copy_(o, non_blocking=True)
+        reset_context()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(x):
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    for i in range(args.warmup):
+        step_resident(i)
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    # ---- timed region: K steps, inputs resident in HBM ----
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    launches0 = lib.b200_launch_count()
+    barrier()
+    t0.record()
+    for i in range(args.steps):
+        step_resident(args.warmup + i, evs[i])
+    t1.record()
+    barrier()
+    launches = lib.b200_launch_count() - launches0
+    ms_total = max_over_ranks(t0.elapsed_time(t1))
+    dec_ms = statistics.mean(a.elapsed_time(b_) for a, b_ in evs)
+    dec_ms = max_over_ranks(dec_ms)
+    # ---- end to end through the layer's forward, host buffers in, host result out ----
+    for i in range(max(3, args.warmup)):
+        step_e2e(i)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    wall0 = time.perf_counter()
+    e0.record()
+    for i in range(args.steps):
+        step_e2e(i)
+    e1.record()
+    barrier()
+    wall_ms = (time.perf_counter() - wall0) * 1e3
+    e2e_ms = max_over_ranks(max(e0.elapsed_time(e1), wall_ms))
+    clocks = sampler.stop() if rank == 0 else None
+    _lib.check(lib.b200_device_status())
+
+    ms_per_step = ms_total / args.steps
+    value = world * step_bytes / (ms_per_step * 1e-3) / 1e9
+    pk = peaks()
+    achieved = dec_bytes / (dec_ms * 1e-3) / 1e9
+    out = {
+        "metric": "paged_decode_attn_hbm_gbs", "value": round(value, 1), "unit": "GB/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_per_step, 5), "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": args.workload, "num_heads": w["H"], "num_kv_heads": w["Hkv"], "head_dim": d,
+                   "batch": b, "context_lens": f"uniform[{w['lo']},{w['hi']}] seed {w['seed']}",
+                   "sum_context": int(lens.sum()), "block_size": BLOCK, "num_blocks": nb,
+                   "parallelism": f"tp{world} by kv head ({hkv} kv heads per GPU), no collective",
+                   "step": "store_kvcache(1 token/seq) + paged decode attention, one layer",
+                   "l2": f"inputs larger than L2: steps rotate over {layers} layer caches "
+                         f"({layers * 2 * nb * BLOCK * hkv * d * 2 / 1e9:.2f} GB per GPU)",
+                   "bytes_per_step_per_gpu": step_bytes},
+        "roofline": {"bound": "hbm", "kernel": "decode_attn_kernel", "achieved": round(achieved, 1),
+                     "peak": pk["hbm"], "unit": "GB/s", "frac": round(achieved / pk["hbm"], 4),
+                     "peak_source": pk["source"], "frac_of_spec_8000": round(achieved / 8000.0, 4),
+                     "algorithmic_bytes_per_launch": dec_bytes, "avg_launch_ms": round(dec_ms, 5),
+                     "traffic": TRAFFIC.get(args.workload) if world == 1 else None},
+        "e2e": {"value": round(world * step_bytes / (e2e_ms / args.steps * 1e-3) / 1e9, 1), "unit": "GB/s",
+                "ms_per_step": round(e2e_ms / args.steps, 5),
+                "h2d_bytes_per_step": int(hq.nbytes + hk.nbytes + hv.nbytes + h_slots.nbytes + h_lens.nbytes + h_bt.nbytes),
+                "d2h_bytes_per_step": int(h_out.nbytes),
+                "api": "nanovllm_b200.Attention.forward with set_context, pinned host q/k/v/metadata in, host output out"},
+        "gpu_launches": int(launches), "clocks": clocks,
+    }
+    if rank == 0 and world == 1:
+        if not args.no_cpu:
+            out["cpu_baseline"] = cpu_decode_baseline(w, sample=64)
+        if not args.no_secondary:
+            out["secondary"] = secondary_prefill(dev)
+    if world > 1:
+        dist.destroy_process_group()
+    return out if rank == 0 else None
+
+
+# dram bytes per launch of the dominant kernel from the committed ncu captures (profiles/), or None
+TRAFFIC = {}
+
+
+# --------------------------------------------------------------------------------------------
+# CPU legs: the oracle timed on the host cores
+# --------------------------------------------------------------------------------------------
+def cpu_decode_baseline(w, sample, repeats=1):
+    from oracle.attention_oracle import decode_algorithmic_bytes, decode_attn_ref, make_block_tables
+    torch.set_num_threads(os.cpu_count() or 1)
+    lens, g = seeded_lens(w)
+    lens = lens[:sample]
+    bt, nb = make_block_tables(lens.tolist(), BLOCK, g)
+    hkv, h, d = w["Hkv"], w["H"], w["D"]
+    kc = (torch.randn(nb, BLOCK, hkv, d, generator=g) * 0.5).to(torch.bfloat16)
+    vc = (torch.randn(nb, BLOCK, hkv, d, generator=g) * 0.5).to(torch.bfloat16)
+    q = (torch.randn(len(lens), h, d, generator=g) * 0.5).to(torch.bfloat16)
+    decode_attn_ref(q[:4], kc, vc, lens[:4], bt[:4], d ** -0.5)
+    t0 = time.perf_counter()
+    for _ in range(repeats):
+        decode_attn_ref(q, kc, vc, lens, bt, d ** -0.5)
+    dt = (time.perf_counter() - t0) / repeats
+    nbytes = decode_algorithmic_bytes(lens, h, hkv, d)
+    return {"value": round(nbytes / dt / 1e9, 3), "unit": "GB/s", "cores": torch.get_num_threads(), "kind": "port",
+            "sample": f"first {len(lens)} of {w['batch']} sequences of the workload, fp32 math on bf16 data, "
+                      f"{dt:.2f} s per pass", "seconds_per_pass": dt, "bytes_per_pass": nbytes}
+
+
+def run_reference(args, w, rank, world):
+    if rank != 0:
+        return None
+    if w["kind"] != "decode":
+        raise SystemExit("--impl reference supports the decode workloads")
+    sample = 64
+    for _ in range(min(args.warmup, 1)):
+        cpu_decode_baseline(w, sample=8)
+    res = cpu_decode_baseline(w, sample=sample, repeats=args.steps)
+    ms = res["seconds_per_pass"] * 1e3
+    return {
+        "impl": "reference", "metric": "paged_decode_attn_hbm_gbs", "value": res["value"], "unit": "GB/s",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms, 3),
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": args.workload, "num_heads": w["H"], "num_kv_heads": w["Hkv"], "head_dim": w["D"],
+                   "batch": w["batch"], "step": f"decode attention of a {sample}-sequence sample on the host cores "
+                                                 "(the reference has no CPU path of its own; this is the oracle port)"},
+        "cpu_baseline": {k: res[k] for k in ("value", "unit", "cores", "kind", "sample")},
+        "e2e": {"value": res["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+
+
+# --------------------------------------------------------------------------------------------
+# prefill (secondary metric; also a workload of its own)
+# --------------------------------------------------------------------------------------------
+def prefill_inputs(dev, w=None):
+    w = w or WORKLOADS["prefill_cfg3"]
+    lens, g = seeded_lens(w)
+    cu = torch.zeros(w["batch"] + 1, dtype=torch.int32)
+    cu[1:] = lens.cumsum(0)
+    t = int(cu[-1])
+    gd = torch.Generator(device=dev).manual_seed(77)
+    q = torch.randn(t, w["H"], w["D"], device=dev, dtype=torch.bfloat16, generator=gd)
+    k = torch.randn(t, w["Hkv"], w["D"], device=dev, dtype=torch.bfloat16, generator=gd)
+    v = torch.randn(t, w["Hkv"], w["D"], device=dev, dtype=torch.bfloat16, generator=gd)
+    return w, lens, cu.to(dev), q, k, v
+
+
+def secondary_prefill(dev, iters=10):
+    import nanovllm_b200
+    from oracle.attention_oracle import prefill_algorithmic_flops
+    w, lens, cu, q, k, v = prefill_inputs(dev)
+    flops = prefill_algorithmic_flops(lens.tolist(), lens.tolist(), w["H"], w["D"])
+    mx = int(lens.max())
+    f = lambda: nanovllm_b200.prefill_attention(q, k, v, cu, cu, mx, mx, w["D"] ** -0.5, w["Hkv"])
+    for _ in range(3):
+        f()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(iters):
+        f()
+    b.record()
+    torch.cuda.synchronize()
+    ms = a.elapsed_time(b) / iters
+    pk = peaks()
+    tf = flops / (ms * 1e-3) / 1e12
+    return {"metric": "prefill_attn_tflops", "workload": "prefill_cfg3 (256 seqs, len uniform[100,1024], dense K/V, causal)",
+            "value": round(tf, 1), "unit": "TFLOP/s", "ms": round(ms, 4), "flops": flops,
+            "frac_of_bf16_peak": round(tf / pk["bf16"], 4), "peak": pk["bf16"], "peak_source": pk["source"],
+            "frac_of_spec_2250": round(tf / 2250.0, 4)}
+
+
+def run_prefill(args, w, rank, world, local):
+    if world != 1:
+        raise SystemExit("prefill_cfg3 is a single-GPU workload")
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    s = secondary_prefill(dev, iters=args.steps)
+    return {"metric": s["metric"], "value": s["value"], "unit": s["unit"], "n_gpus": 1, "steps": args.steps,
+            "warmup": 3, "ms_per_step": s["ms"], "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic", "config": {"workload": s["workload"]},
+            "roofline": {"bound": "tensor", "achieved": s["value"], "peak": s["peak"], "unit": "TFLOP/s",
+                         "frac": s["frac_of_bf16_peak"], "peak_source": s["peak_source"], "traffic": None}}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="decode_cfg2", choices=list(WORKLOADS))
+    ap.add_argument("--no-secondary", action="store_true", help="skip the prefill side measurement")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--layers", type=int, default=0, help="layer caches the steps rotate over (0 = workload default)")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    rank, world, local = dist_env()
+    if world != args.gpus and world == 1 and args.gpus > 1:
+        raise SystemExit("launch with torch.distributed.run --nproc-per-node %d for --gpus %d" % (args.gpus, args.gpus))
+    w = WORKLOADS[args.workload]
+    if args.impl == "reference":
+        res = run_reference(args, w, rank, world)
+    elif w["kind"] == "decode":
+        res = run_decode(args, w, rank, world, local)
+    else:
+        res = run_prefill(args, w, rank, world, local)
+    if res is not None:
+        print(json.dumps(res), flush=True)
+
+
+if __name__ == "__main__":
+    main()

@@ -21,18 +21,19 @@ import sys
 
 def install():
     from .layers import attention as ours
-    ref_ctx = importlib.import_module("nanovllm.utils.context")
-    ours.set_context_getter(ref_ctx.get_context)
     ref_attn = sys.modules.get("nanovllm.layers.attention")
     if ref_attn is None:
-        # Register our module under the reference's name so that importing it never pulls in
-        # Triton or flash_attn.
+        # Register this package's module under the reference's name BEFORE nano-vllm is imported,
+        # so that its own attention file (and with it Triton and flash_attn) is never executed.
         sys.modules["nanovllm.layers.attention"] = ours
-        layers_pkg = importlib.import_module("nanovllm.layers")
-        setattr(layers_pkg, "attention", ours)
-    else:
+    elif ref_attn is not ours:
         ref_attn.Attention = ours.Attention
         ref_attn.store_kvcache = ours.store_kvcache
+    ref_ctx = importlib.import_module("nanovllm.utils.context")
+    ours.set_context_getter(ref_ctx.get_context)
+    layers_pkg = importlib.import_module("nanovllm.layers")
+    if sys.modules["nanovllm.layers.attention"] is ours:
+        setattr(layers_pkg, "attention", ours)
     qwen3 = sys.modules.get("nanovllm.models.qwen3")
     if qwen3 is not None:
         qwen3.Attention = ours.Attention
