@@ -81,6 +81,33 @@ int b200_decode_attn(const void* q, int64_t q_row_stride, const void* k_cache, c
                      int64_t workspace_bytes, int32_t batch, int32_t num_heads, int32_t num_kv_heads,
                      int32_t head_dim, float scale, void* stream);
 
+/* No counterpart in the reference: decode attention for callers that cannot allocate.
+ *
+ * b200_decode_attn needs a caller-owned workspace.  Some callers have no way to provide one: an
+ * engine that has already given all free device memory to its KV cache (a later cudaMalloc may
+ * fail), a plugin interface that forbids allocating inside the call, code that must stay away from
+ * the framework's allocator.  This variant computes exactly what b200_decode_attn computes, with
+ * the same arguments minus the workspace, and keeps its scratch inside the library: a __device__
+ * array of b200_decode_static_scratch_bytes() (about 5.1 MiB) that every GPU which loads the
+ * library holds until the process exits.  It calls no cudaMalloc/cudaFree and no allocating
+ * library routine.
+ *
+ * Limits (rejected with B200_ERR_WORKSPACE and a message, nothing launched): the device may run at
+ * most 320 persistent CTAs (2 per multiprocessor: up to 160 SMs), and min(batch, 1024) *
+ * num_kv_heads may be at most 8192.  Beyond that use b200_decode_attn.
+ *
+ * The first call on each device looks up the array's device address (cudaGetSymbolAddress, with
+ * that device current); make that first call before any stream capture begins.  All calls on a
+ * device share the one array: it keeps the previous call's contents (the entry point clears the
+ * part that must start at zero, on `stream`, before launching), and two calls that overlap on
+ * the GPU -- different streams, or different host threads -- race on it.  Serialise them. */
+int64_t b200_decode_static_scratch_bytes(void);
+int b200_decode_attn_static(const void* q, int64_t q_row_stride, const void* k_cache, const void* v_cache,
+                            int64_t num_blocks, int32_t block_size, const int32_t* block_tables,
+                            int64_t bt_row_stride, int32_t bt_cols, const int32_t* context_lens, void* out,
+                            int32_t batch, int32_t num_heads, int32_t num_kv_heads, int32_t head_dim, float scale,
+                            void* stream);
+
 /* Replaces flash_attn_varlen_func as called for prefill (nanovllm/layers/attention.py:64-70).
  * Sequence i owns query rows cu_seqlens_q[i] .. cu_seqlens_q[i+1] of q (total_q, num_heads, 128)
  * and keys 0 .. Lk_i - 1 with Lk_i = cu_seqlens_k[i+1] - cu_seqlens_k[i].  Causal mask aligned

@@ -23,6 +23,10 @@ SIGNATURES = {
     "b200_decode_attn": (c_int32, [c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_int32, c_void_p, c_int64,
                                    c_int32, c_void_p, c_void_p, c_void_p, c_int64, c_int32, c_int32, c_int32,
                                    c_int32, c_float, c_void_p]),
+    "b200_decode_static_scratch_bytes": (c_int64, []),
+    "b200_decode_attn_static": (c_int32, [c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_int32, c_void_p, c_int64,
+                                          c_int32, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32, c_float,
+                                          c_void_p]),
     "b200_prefill_attn": (c_int32, [c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p,
                                     c_void_p, c_int64, c_int32, c_void_p, c_int64, c_int32, c_void_p, c_void_p,
                                     c_int32, c_int32, c_int32, c_int32, c_void_p, c_int32, c_int32, c_int32,

@@ -522,3 +522,86 @@ extern "C" int b200_decode_attn(const void* q, int64_t q_row_stride, const void*
   }
   return kOk;
 }
+
+// ---------------------------------------------------------------------------------------------
+// Decode attention for callers that cannot allocate device memory.
+//
+// Some hosts of this library have nowhere to get a workspace from: a serving engine that has
+// already handed every free byte of the GPU to its KV cache (nano-vllm sizes the cache from the
+// free memory it finds, so a later cudaMalloc can fail), a plugin slot whose contract forbids
+// allocation inside the call, or code that runs where the framework's caching allocator must not
+// be touched.  For them the scratch of the decode kernel lives in the library image itself: a
+// file-scope __device__ array that every GPU loading the library holds until the process exits.
+// ---------------------------------------------------------------------------------------------
+namespace b200 {
+
+constexpr int kStaticMaxGrid = 320;        // persistent CTAs the static scratch has partial slots for
+constexpr int kStaticMaxCounters = 8192;   // (sequence, kv head) pairs per launch: min(batch, 1024) * Hkv
+constexpr long long kStaticScratchBytes =
+    kWsStatusBytes + static_cast<long long>(kStaticMaxGrid) * 2 * kMaxG * 130 * 4 + kStaticMaxCounters * 4;
+
+static __device__ __align__(256) unsigned char g_decode_static_scratch[kStaticScratchBytes];
+
+// Device address of the array above on the current device.  In host code the array's name is only a
+// handle for the runtime, never an address a kernel may be given, so the address is asked for
+// once per device (with that device current) and remembered.
+static int static_scratch_address(void** out) {
+  static void* cached[64];
+  static std::atomic<int> ready[64];
+  int dev = 0;
+  int rc = check_cuda(cudaGetDevice(&dev), "decode_attn_static: cudaGetDevice");
+  if (rc) return rc;
+  if (dev < 0 || dev >= 64) return set_error(kErrDevice, "decode_attn_static: device ordinal %d not supported", dev);
+  if (!ready[dev].load(std::memory_order_acquire)) {
+    void* ptr = nullptr;
+    rc = check_cuda(cudaGetSymbolAddress(&ptr, g_decode_static_scratch), "decode_attn_static: cudaGetSymbolAddress");
+    if (rc) return rc;
+    if (!ptr) return set_error(kErrDevice, "decode_attn_static: the scratch array has no address on device %d", dev);
+    cached[dev] = ptr;
+    ready[dev].store(1, std::memory_order_release);
+  }
+  *out = cached[dev];
+  return kOk;
+}
+
+}  // namespace b200
+
+extern "C" int64_t b200_decode_static_scratch_bytes(void) { return b200::kStaticScratchBytes; }
+
+extern "C" int b200_decode_attn_static(const void* q, int64_t q_row_stride, const void* k_cache, const void* v_cache,
+                                       int64_t num_blocks, int32_t block_size, const int32_t* block_tables,
+                                       int64_t bt_row_stride, int32_t bt_cols, const int32_t* context_lens, void* out,
+                                       int32_t batch, int32_t num_heads, int32_t num_kv_heads, int32_t head_dim,
+                                       float scale, void* stream) {
+  using namespace b200;
+  if (batch < 0) return set_error(kErrBadShape, "decode_attn_static: negative batch");
+  if (batch == 0) return kOk;
+  if (num_heads <= 0 || num_kv_heads <= 0 || num_heads % num_kv_heads)
+    return set_error(kErrBadShape, "decode_attn_static: num_heads (%d) must be a positive multiple of num_kv_heads (%d)",
+                     num_heads, num_kv_heads);
+  const int grid = decode_grid();
+  if (grid <= 0) return set_error(kErrNoDriver, "decode_attn_static: no CUDA device");
+  if (grid > kStaticMaxGrid)
+    return set_error(kErrWorkspace,
+                     "decode_attn_static: this GPU runs %d persistent CTAs but the built-in scratch has room for %d; "
+                     "use b200_decode_attn with a caller-owned workspace", grid, kStaticMaxGrid);
+  const long long per_launch = batch < kDecMaxBatch ? batch : kDecMaxBatch;
+  if (per_launch * num_kv_heads > kStaticMaxCounters)
+    return set_error(kErrWorkspace,
+                     "decode_attn_static: min(batch, %d) * num_kv_heads = %lld exceeds the built-in scratch's limit of %d; "
+                     "use b200_decode_attn with a caller-owned workspace", kDecMaxBatch, per_launch * num_kv_heads,
+                     kStaticMaxCounters);
+  void* scratch = nullptr;
+  int rc = static_scratch_address(&scratch);
+  if (rc) return rc;
+  // The array keeps whatever the previous call left.  Partials are always written before they are
+  // read; the arrival counters are the one part that must start at zero, so clear them here.
+  unsigned char* counters = static_cast<unsigned char*>(scratch) + kWsStatusBytes + decode_partial_bytes(grid);
+  rc = check_cuda(cudaMemsetAsync(counters, 0, static_cast<size_t>(per_launch) * num_kv_heads * 4,
+                                  static_cast<cudaStream_t>(stream)),
+                  "decode_attn_static: clearing the arrival counters");
+  if (rc) return rc;
+  return b200_decode_attn(q, q_row_stride, k_cache, v_cache, num_blocks, block_size, block_tables, bt_row_stride, bt_cols,
+                          context_lens, out, scratch, kStaticScratchBytes, batch, num_heads, num_kv_heads, head_dim,
+                          scale, stream);
+}
