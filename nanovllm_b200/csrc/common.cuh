@@ -35,11 +35,12 @@ int check_cuda(cudaError_t e, const char* what); // 0 or positive cudaError_t wi
 int sm_count();                                  // multiprocessors of the current device (cached per device)
 
 // Builds a tiled tensor map over a (tokens, heads, 128) bf16 array whose token rows are
-// `row_stride_elems` apart: dims {64-wide half of head_dim, head, token}, box {64, 1, box_tokens},
-// 128-byte swizzle.  The same form covers the paged cache (tokens = num_blocks * block_size) and
-// packed q/k/v activations with arbitrary row stride.
+// `row_stride_elems` apart: dims {128 head_dim, head, token}, box {64, box_heads, box_tokens}
+// (one 64-wide half of head_dim; rows of the box ordered token-major, head-minor), 128-byte
+// swizzle.  The same form covers the paged cache (tokens = num_blocks * block_size) and packed
+// q/k/v activations with arbitrary row stride.
 int make_tokens_heads_map(CUtensorMap* map, const void* base, uint64_t tokens, uint32_t heads,
-                          uint64_t row_stride_elems, uint32_t box_tokens);
+                          uint64_t row_stride_elems, uint32_t box_tokens, uint32_t box_heads = 1);
 
 #ifdef __CUDACC__
 

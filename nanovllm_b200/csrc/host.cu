@@ -56,13 +56,13 @@ static EncodeTiledFn encode_fn() {
 }
 
 int make_tokens_heads_map(CUtensorMap* map, const void* base, uint64_t tokens, uint32_t heads,
-                          uint64_t row_stride_elems, uint32_t box_tokens) {
+                          uint64_t row_stride_elems, uint32_t box_tokens, uint32_t box_heads) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return set_error(kErrNoDriver, "cuTensorMapEncodeTiled is not available (no CUDA driver?)");
   if (tokens == 0) tokens = 1;  // an empty tensor is never read; keep the encoder happy
   cuuint64_t dims[3] = {128, heads, tokens};
   cuuint64_t strides[2] = {128 * 2, row_stride_elems * 2};
-  cuuint32_t box[3] = {64, 1, box_tokens};
+  cuuint32_t box[3] = {64, box_heads, box_tokens};
   cuuint32_t estr[3] = {1, 1, 1};
   CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -88,9 +88,9 @@ int b200_device_status(void) {
     cudaError_t e = cudaGetLastError();
     return b200::check_cuda(e == cudaSuccess ? cudaErrorUnknown : e, "device_status: cudaDeviceSynchronize");
   }
-  if (b200::read_status_decode() || b200::read_status_prefill_mma())
-    return b200::set_error(b200::kErrTimeout, "a bounded device-side wait gave up (decode=%d prefill=%d)",
-                           b200::read_status_decode(), b200::read_status_prefill_mma());
+  if (b200::read_status_decode() || b200::read_status_prefill_mma() || b200::read_status_prefill_tc())
+    return b200::set_error(b200::kErrTimeout, "a bounded device-side wait gave up (decode=%d prefill mma=%d tcgen05=%d)",
+                           b200::read_status_decode(), b200::read_status_prefill_mma(), b200::read_status_prefill_tc());
   return b200::kOk;
 }
 

@@ -22,10 +22,16 @@ struct PrefillParams {
   float scale_log2;
 };
 
+// mma.sync variant: K/V maps with 64-token boxes.
 int launch_prefill_mma(const PrefillParams& p, const CUtensorMap& map_k, const CUtensorMap& map_v, cudaStream_t stream);
+// tcgen05 variant: Q map with a {64, G, 128 / G} box, K/V maps with 128-token boxes; needs 128 % G == 0.
+bool prefill_tc_supports(const PrefillParams& p);
+int launch_prefill_tc(const PrefillParams& p, const CUtensorMap& map_q, const CUtensorMap& map_k,
+                      const CUtensorMap& map_v, cudaStream_t stream);
 
 // Device-side "a bounded wait gave up" flags, one per translation unit, summed by b200_device_status().
 int read_status_decode();
 int read_status_prefill_mma();
+int read_status_prefill_tc();
 
 }  // namespace b200

@@ -27,6 +27,13 @@ extern "C" int b200_prefill_attn(const void* q, int64_t q_row_stride, const void
   if (max_seqlen_q <= 0 || max_seqlen_k <= 0)
     return set_error(kErrBadShape, "prefill_attn: max_seqlen_q/k must be positive");
 
+  if (kernel_variant < 0 || kernel_variant > 2)
+    return set_error(kErrBadShape, "prefill_attn: kernel_variant must be 0, 1 or 2");
+  const bool tc_ok = 128 % G == 0;
+  if (kernel_variant == 2 && !tc_ok)
+    return set_error(kErrBadShape, "prefill_attn: the tcgen05 kernel needs 128 %% (num_heads / num_kv_heads) == 0 (got %d)", G);
+  const bool use_tc = kernel_variant == 2 || (kernel_variant == 0 && tc_ok);
+  const uint32_t kv_box = use_tc ? 128 : 64;
   CUtensorMap map_k, map_v;
   const bool paged = block_tables != nullptr;
   int rc;
@@ -41,9 +48,9 @@ extern "C" int b200_prefill_attn(const void* q, int64_t q_row_stride, const void
     if ((reinterpret_cast<uintptr_t>(k_cache) | reinterpret_cast<uintptr_t>(v_cache)) & 15)
       return set_error(kErrMisaligned, "prefill_attn: caches must be 16-byte aligned");
     const uint64_t rows = static_cast<uint64_t>(num_blocks) * block_size;
-    rc = make_tokens_heads_map(&map_k, k_cache, rows, num_kv_heads, static_cast<uint64_t>(num_kv_heads) * 128, 64);
+    rc = make_tokens_heads_map(&map_k, k_cache, rows, num_kv_heads, static_cast<uint64_t>(num_kv_heads) * 128, kv_box);
     if (rc) return rc;
-    rc = make_tokens_heads_map(&map_v, v_cache, rows, num_kv_heads, static_cast<uint64_t>(num_kv_heads) * 128, 64);
+    rc = make_tokens_heads_map(&map_v, v_cache, rows, num_kv_heads, static_cast<uint64_t>(num_kv_heads) * 128, kv_box);
     if (rc) return rc;
   } else {
     if (!k || !v) return set_error(kErrNullPointer, "prefill_attn: dense k/v missing");
@@ -53,9 +60,9 @@ extern "C" int b200_prefill_attn(const void* q, int64_t q_row_stride, const void
       return set_error(kErrMisaligned, "prefill_attn: k/v row strides must be >= Hkv*128 and multiples of 8 elements");
     if ((reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v)) & 15)
       return set_error(kErrMisaligned, "prefill_attn: k and v must be 16-byte aligned");
-    rc = make_tokens_heads_map(&map_k, k, static_cast<uint64_t>(total_k), num_kv_heads, static_cast<uint64_t>(k_row_stride), 64);
+    rc = make_tokens_heads_map(&map_k, k, static_cast<uint64_t>(total_k), num_kv_heads, static_cast<uint64_t>(k_row_stride), kv_box);
     if (rc) return rc;
-    rc = make_tokens_heads_map(&map_v, v, static_cast<uint64_t>(total_k), num_kv_heads, static_cast<uint64_t>(v_row_stride), 64);
+    rc = make_tokens_heads_map(&map_v, v, static_cast<uint64_t>(total_k), num_kv_heads, static_cast<uint64_t>(v_row_stride), kv_box);
     if (rc) return rc;
   }
 
@@ -80,7 +87,12 @@ extern "C" int b200_prefill_attn(const void* q, int64_t q_row_stride, const void
   p.total_q = total_q;
   p.max_seqlen_q = max_seqlen_q;
   p.max_seqlen_k = max_seqlen_k;
-  if (kernel_variant < 0 || kernel_variant > 2)
-    return set_error(kErrBadShape, "prefill_attn: kernel_variant must be 0, 1 or 2");
+  if (use_tc) {
+    CUtensorMap map_q;
+    rc = make_tokens_heads_map(&map_q, q, static_cast<uint64_t>(total_q), num_heads, static_cast<uint64_t>(q_row_stride),
+                               static_cast<uint32_t>(p.QT), static_cast<uint32_t>(G));
+    if (rc) return rc;
+    return launch_prefill_tc(p, map_q, map_k, map_v, static_cast<cudaStream_t>(stream));
+  }
   return launch_prefill_mma(p, map_k, map_v, static_cast<cudaStream_t>(stream));
 }

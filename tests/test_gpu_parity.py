@@ -285,16 +285,27 @@ def _prefill_case(seed, lens, prefix, h, hkv, paged, poison=True):
     return q, kc, vc, cu_q, cu_k, bt, None
 
 
+VARIANTS = {"mma": 1, "tcgen05": 2}
+
+
+def _variants(h, hkv):
+    g = h // hkv
+    return ["mma"] + (["tcgen05"] if 128 % g == 0 else [])
+
+
+@pytest.mark.parametrize("variant", ["mma", "tcgen05"])
 @pytest.mark.parametrize("h,hkv", [(16, 8), (4, 1), (2, 2), (5, 1), (8, 1)])
-def test_prefill_dense_ragged(b200, h, hkv):
+def test_prefill_dense_ragged(b200, h, hkv, variant):
     pkg, _ = b200
+    if variant not in _variants(h, hkv):
+        pytest.skip("the tcgen05 kernel needs 128 % G == 0")
     lens = [1, 2, 63, 64, 65, 127, 128, 129, 500, 1024, 31]
     q, k, v, cu_q, cu_k, _, fused = _prefill_case(31 + h, lens, [0] * len(lens), h, hkv, paged=False)
     fd = fused.to(DEV)
     kd = k.to(DEV)
     vd = fd[:, hkv * 128:].view(-1, hkv, 128)
     out = pkg.prefill_attention(q.to(DEV), kd, vd, cu_q.to(DEV), cu_k.to(DEV), max(lens), max(lens),
-                                default_scale(128), hkv)
+                                default_scale(128), hkv, kernel_variant=VARIANTS[variant])
     torch.cuda.synchronize()
     want = prefill_attn_ref(q, k, v, cu_q, cu_k, default_scale(128))
     assert torch.isfinite(out.float()).all()
@@ -302,15 +313,16 @@ def test_prefill_dense_ragged(b200, h, hkv):
     _status_ok()
 
 
+@pytest.mark.parametrize("variant", ["mma", "tcgen05"])
 @pytest.mark.parametrize("h,hkv", [(16, 8), (4, 1), (2, 2)])
-def test_prefill_paged_prefix_poisoned(b200, h, hkv):
+def test_prefill_paged_prefix_poisoned(b200, h, hkv, variant):
     pkg, _ = b200
     lens = [300, 600, 513, 256, 700, 1025, 512, 40]
     prefix = [0, 256, 512, 0, 512, 768, 512, 0]          # one sequence fully cached: no query rows
     q, kc, vc, cu_q, cu_k, bt, _ = _prefill_case(41 + h, lens, prefix, h, hkv, paged=True)
     lq = [a - b for a, b in zip(lens, prefix)]
     out = pkg.prefill_attention(q.to(DEV), kc.to(DEV), vc.to(DEV), cu_q.to(DEV), cu_k.to(DEV), max(lq), max(lens),
-                                default_scale(128), hkv, block_tables=bt.to(DEV))
+                                default_scale(128), hkv, block_tables=bt.to(DEV), kernel_variant=VARIANTS[variant])
     torch.cuda.synchronize()
     want = prefill_attn_ref(q, kc, vc, cu_q, cu_k, default_scale(128), bt)
     assert torch.isfinite(out.float()).all()
