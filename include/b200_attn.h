@@ -88,13 +88,14 @@ int b200_decode_attn(const void* q, int64_t q_row_stride, const void* k_cache, c
  * fail), a plugin interface that forbids allocating inside the call, code that must stay away from
  * the framework's allocator.  This variant computes exactly what b200_decode_attn computes, with
  * the same arguments minus the workspace, and keeps its scratch inside the library: a __device__
- * array of b200_decode_static_scratch_bytes() (about 5.1 MiB) that every GPU which loads the
+ * array of b200_decode_static_scratch_bytes() (about 8.4 MiB) that every GPU which loads the
  * library holds until the process exits.  It calls no cudaMalloc/cudaFree and no allocating
  * library routine.
  *
- * Limits (rejected with B200_ERR_WORKSPACE and a message, nothing launched): the device may run at
- * most 320 persistent CTAs (2 per multiprocessor: up to 160 SMs), and min(batch, 1024) *
- * num_kv_heads may be at most 8192.  Beyond that use b200_decode_attn.
+ * Limits (rejected with B200_ERR_WORKSPACE and a message, nothing launched): (persistent CTAs of
+ * the device = 2 per multiprocessor) x (num_heads / num_kv_heads) may be at most 1280 -- on a
+ * 148-SM B200 that is up to 4 query heads per kv head -- and num_kv_heads at most 128.  Beyond
+ * that use b200_decode_attn.
  *
  * The first call on each device looks up the array's device address (cudaGetSymbolAddress, with
  * that device current); make that first call before any stream capture begins.  All calls on a

@@ -3,20 +3,29 @@
 //
 // HBM-bound: every K and V byte of every context token is read exactly once.  Design:
 //  * Work unit = one 64-token tile of one (sequence, kv head).  The tiles of all sequences and
-//    heads form one flat list; the persistent grid (2 CTAs per SM) cuts that list into equal
-//    contiguous ranges, so every CTA streams the same number of bytes whatever the length
-//    distribution.  The list is derived on the device from context_lens (a block scan per CTA):
-//    the launch geometry never depends on device data, as CUDA-graph replay requires.
-//  * A producer warp walks the range and issues TMA tile loads (two 64x64 boxes for K, two for
-//    V, 128-byte swizzle) into a ring of shared-memory stages guarded by full/empty mbarriers;
-//    the ring never drains at sequence boundaries.
+//    heads form one flat list (sequence -> head -> tile), derived on the device from context_lens
+//    by a block scan in every CTA: the launch geometry never depends on device data, as CUDA-graph
+//    replay requires.  The list is cut into contiguous PIECES: one equal static piece per CTA
+//    of the persistent grid (2 CTAs per SM) covering about 70 % of the tiles, then one larger and
+//    four smaller pieces per CTA handed out through an atomic ticket counter, so that CTAs that
+//    stream faster take more of the tail and all finish together.
+//  * The producer warp (one elected lane) walks its pieces.  For every (sequence, head) segment it
+//    publishes a descriptor in shared memory, bulk-copies the segment's G query rows into a small
+//    ring, and issues the TMA tile loads (two 64x64 boxes for K, two for V, 128-byte swizzle;
+//    16-token boxes for the ragged last tile of a sequence) into a ring of stages guarded by
+//    full/empty mbarriers.  The descriptor and the query rows ride on the full-barrier of the
+//    segment's first tile, and metadata of the next segment is fetched one segment ahead, so the
+//    ring never drains at sequence or piece boundaries.
 //  * Four consumer warps take 16 tokens of each tile: QK^T and PV on mma.sync.m16n8k16 (the G
 //    query heads of the kv head are rows of the 16-row A operand), online softmax in fp32 with
-//    quad shuffles, then a cross-warp combine in shared memory.
-//  * A (sequence, head) cut by range boundaries leaves per-CTA partials (m, l, unnormalised O) in
-//    the workspace; the last CTA to arrive (one atomic counter per (sequence, head), reset by that
-//    CTA) merges them.  No CTA ever waits for another.
+//    quad shuffles.  At the end of a segment they only drop their running (m, l, O) into shared
+//    memory and go on with the next tile.
+//  * An epilogue warp combines the four warps' states and writes the bf16 row, or, where a piece
+//    boundary cuts the (sequence, head), a partial (m, l, unnormalised O) to the workspace; the
+//    last piece to arrive (one atomic counter per (sequence, head), reset by that warp) merges the
+//    partials.  No CTA ever waits for another; every mbarrier wait is bounded.
 #include <atomic>
+#include <cstdlib>
 
 #include "../../include/b200_attn.h"
 #include "kernels.cuh"
@@ -30,11 +39,16 @@ constexpr int kStageBytes = 4 * kSubTileBytes;  // K lo, K hi, V lo, V hi
 constexpr int kDecStages = 3;
 constexpr int kDecConsumerWarps = 4;
 constexpr int kDecConsumers = kDecConsumerWarps * 32;
-constexpr int kDecThreads = kDecConsumers + 32;
-constexpr int kDecMaxBatch = 1024;              // per launch; the host splits larger batches
+constexpr int kDecProducerWarp = kDecConsumerWarps;
+constexpr int kDecEpilogueWarp = kDecConsumerWarps + 1;
+constexpr int kDecThreads = kDecConsumers + 64;
+constexpr int kDecMaxBatch = 512;               // per launch; the host splits larger batches
 constexpr int kDecPer = (kDecMaxBatch + kDecThreads - 1) / kDecThreads;
 constexpr int kMaxG = 16;
-constexpr int kWsStatusBytes = 256;  // reserved header
+constexpr int kWsStatusBytes = 256;  // header: word 0 is the ticket counter of the piece scheduler
+constexpr int kWsCounterInts = kDecMaxBatch * 128;   // arrival counters: fixed region, up to 128 kv heads
+constexpr int kSegRing = kDecStages + 1;   // segment descriptors / query rows in flight
+constexpr int kDecPending = 8;             // partials written but not yet counted, per CTA
 static __device__ int g_status_decode = 0;
 
 struct DecodeParams {
@@ -49,37 +63,150 @@ struct DecodeParams {
   int block_size;
   long long num_blocks;
   float scale_log2;
-  float* ws_o;    // [2 * grid][G][128] unnormalised partial outputs
-  float* ws_ml;   // [2 * grid][G][2]   running max (log2 domain) and sum
+  int n_merge;    // hand-off buffers between the consumer warps and the epilogue warp (1 or 2)
+  int dyn_factor; // work per CTA (tiles) from which the dynamic tail is used
+  int big_pct, small_pct100, small_n;  // geometry of the dynamic tail
+  float* ws_o;    // [2 * pieces][G][128] unnormalised partial outputs
+  float* ws_ml;   // [2 * pieces][G][2]   running max (log2 domain) and sum
   int* counters;  // [batch * Hkv], zero between launches
+  unsigned int* ticket;  // piece scheduler, zero between launches
 };
 
-__device__ __forceinline__ int dec_merge_floats(int G) { return kDecConsumerWarps * G * 128; }
+// Optional per-CTA timestamps (compile with -DB200_TRACE; read with b200_debug_trace).  Off by default.
+#ifdef B200_TRACE
+__device__ unsigned long long g_dec_trace[1024 * 8];
+__device__ __forceinline__ unsigned long long trace_now() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+#define DEC_TRACE(slot) do { g_dec_trace[blockIdx.x * 8 + (slot)] = trace_now(); } while (0)
+#else
+#define DEC_TRACE(slot) do { } while (0)
+#endif
+
+// One (sequence, kv head) segment inside one piece, as the producer hands it to the other warps.
+struct SegDesc {
+  int seq;               // -1: no more work for this CTA
+  int h;
+  int t0, t1;            // tiles [t0, t1) of the (sequence, head) that lie in the piece
+  int nt;                // tiles of the whole (sequence, head)
+  int len;               // context length, clamped to the block table's capacity
+  int slot;              // workspace slot for a partial: 2 * piece + (does the piece start inside it ? 0 : 1)
+  int pad;
+  long long seg_start;   // flat position of tile 0 of the (sequence, head)
+};
+
+// How the flat tile list [0, T) is cut into pieces.  Pieces are numbered in list order:
+//   [0, g)            static, one per CTA, equal sizes, together the first Ts tiles;
+//   [g, g + nb)       "big" dynamic pieces of Cb tiles;
+//   [g + nb, total)   "small" dynamic pieces of Cs tiles, ending exactly at T.
+// Every CTA computes the same geometry from T and the grid size.
+struct DecPieces {
+  long long T, Ts, Tb_end;
+  int g, nb, ns, Cb, Cs;
+  __device__ __forceinline__ int dynamic() const { return nb + ns; }
+  __device__ __forceinline__ long long start(int i) const {
+    if (i < g) return static_cast<long long>(i) * Ts / g;
+    if (i < g + nb) return Ts + static_cast<long long>(i - g) * Cb;
+    return Tb_end + static_cast<long long>(i - g - nb) * Cs;
+  }
+  __device__ __forceinline__ int of(long long x) const {
+    if (x < Ts) return static_cast<int>(((x + 1) * g - 1) / Ts);
+    if (x < Tb_end) return g + static_cast<int>((x - Ts) / Cb);
+    return g + nb + static_cast<int>((x - Tb_end) / Cs);
+  }
+};
+
+__device__ __forceinline__ DecPieces dec_pieces(long long T, int grid, int dyn_factor, int big_pct, int small_pct100,
+                                              int small_n) {
+  DecPieces pc;
+  pc.T = T;
+  pc.g = T < grid ? static_cast<int>(T) : grid;
+  if (T < static_cast<long long>(dyn_factor) * grid) {          // too little work to be worth a dynamic tail
+    pc.Ts = pc.Tb_end = T;
+    pc.nb = pc.ns = 0;
+    pc.Cb = pc.Cs = 1;
+    return pc;
+  }
+  const long long W = T / grid;   // tiles per CTA if all ran at the same speed
+  pc.Cs = static_cast<int>((W * small_pct100 + 5000) / 10000);   // small_pct100 / 100 % of W each, small_n per CTA
+  pc.Cb = static_cast<int>((W * big_pct + 50) / 100);            // big_pct % of W, one per CTA
+  if (pc.Cs < 1) pc.Cs = 1;
+  if (pc.Cb < 1) pc.Cb = 1;
+  pc.nb = grid;
+  pc.ns = small_n * grid;
+  pc.Ts = T - static_cast<long long>(pc.nb) * pc.Cb - static_cast<long long>(pc.ns) * pc.Cs;
+  pc.Tb_end = pc.Ts + static_cast<long long>(pc.nb) * pc.Cb;
+  return pc;
+}
+
+// The segment that starts at flat position x inside a piece [.., r_end).
+__device__ __forceinline__ SegDesc dec_locate(const int* s_prefix, int batch, int Hkv, long long x, long long r_begin,
+                                              long long r_end, int piece) {
+  int lo = 0, hi = batch;
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (static_cast<long long>(s_prefix[mid]) * Hkv <= x) lo = mid; else hi = mid;
+  }
+  SegDesc d;
+  d.seq = lo;
+  d.nt = s_prefix[lo + 1] - s_prefix[lo];
+  const long long rem = x - static_cast<long long>(s_prefix[lo]) * Hkv;
+  d.h = static_cast<int>(rem / d.nt);
+  d.t0 = static_cast<int>(rem - static_cast<long long>(d.h) * d.nt);
+  d.seg_start = x - d.t0;
+  const long long seg_end = d.seg_start + d.nt;
+  const long long my_end = seg_end < r_end ? seg_end : r_end;
+  d.t1 = d.t0 + static_cast<int>(my_end - x);
+  d.slot = piece * 2 + (d.seg_start <= r_begin ? 0 : 1);
+  d.len = 0;
+  d.pad = 0;
+  return d;
+}
+
+// 1-D bulk copy global -> shared, completion counted on an mbarrier (addresses and size multiples of 16).
+__device__ __forceinline__ void bulk_load_1d(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
 
 __global__ void __launch_bounds__(kDecThreads, 2)
 decode_attn_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap map_k,
-                   const __grid_constant__ CUtensorMap map_v) {
+                   const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_k16,
+                   const __grid_constant__ CUtensorMap map_v16) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int G = p.G, Hkv = p.Hkv;
   unsigned char* stages = smem;
-  float* merge_o = reinterpret_cast<float*>(smem + kDecStages * kStageBytes);
-  float* merge_ml = merge_o + dec_merge_floats(p.G);
-  int* s_prefix = reinterpret_cast<int*>(merge_ml + kDecConsumerWarps * p.G * 2);
+  __nv_bfloat16* s_q = reinterpret_cast<__nv_bfloat16*>(smem + kDecStages * kStageBytes);          // [kSegRing][G][128]
+  float* merge_o = reinterpret_cast<float*>(s_q + kSegRing * G * 128);                            // [n_merge][4][G][128]
+  float* merge_ml = merge_o + p.n_merge * kDecConsumerWarps * G * 128;                              // [n_merge][4][G][2]
+  int* s_prefix = reinterpret_cast<int*>(merge_ml + p.n_merge * kDecConsumerWarps * G * 2);       // [batch + 1]
   __shared__ __align__(8) uint64_t bar_full[kDecStages];
   __shared__ __align__(8) uint64_t bar_empty[kDecStages];
+  __shared__ __align__(8) uint64_t bar_merge_full[2];
+  __shared__ __align__(8) uint64_t bar_merge_empty[2];
+  __shared__ __align__(16) SegDesc s_desc[kSegRing];
+  __shared__ __align__(16) SegDesc s_merge_desc[2];
+  __shared__ __align__(16) SegDesc s_pending[kDecPending];
   __shared__ int s_warp_sums[kDecThreads / 32];
   __shared__ int s_abort;
-  __shared__ int s_last;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int G = p.G, Hkv = p.Hkv;
   const int max_len = p.bt_cols * p.block_size;
+  if (tid == 0) DEC_TRACE(0);
 
   if (tid == 0) {
     s_abort = 0;
     for (int s = 0; s < kDecStages; ++s) {
       mbar_init(&bar_full[s], 1);
       mbar_init(&bar_empty[s], kDecConsumerWarps);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&bar_merge_full[s], kDecConsumerWarps);
+      mbar_init(&bar_merge_empty[s], 1);
     }
     mbar_fence_init();
   }
@@ -132,64 +259,268 @@ decode_attn_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap map
     }
   }
 
-  const long long T = static_cast<long long>(s_prefix[p.batch]) * Hkv;  // tile units in this launch
-  const long long grid_eff = T < gridDim.x ? T : gridDim.x;
-  const long long cta = blockIdx.x;
-  if (cta >= grid_eff) return;
-  const long long r_begin = cta * T / grid_eff;
-  const long long r_end = (cta + 1) * T / grid_eff;
+  const long long T = static_cast<long long>(s_prefix[p.batch]) * Hkv;  // tiles in this launch
+  const DecPieces pc = dec_pieces(T, static_cast<int>(gridDim.x), p.dyn_factor, p.big_pct, p.small_pct100, p.small_n);
+  const int cta = blockIdx.x;
+  if (cta >= pc.g) return;
+  if (tid == 0) DEC_TRACE(1);
 
   volatile int* abort_flag = &s_abort;
 
-  if (warp == kDecConsumerWarps) {
+  if (warp == kDecProducerWarp) {
     // =========================== producer warp ===========================
-    if (lane == 0) {
-      tma_prefetch_desc(&map_k);
-      tma_prefetch_desc(&map_v);
-      int it = 0;
-      long long x = r_begin;
-      bool ok = true;
-      while (x < r_end && ok) {
-        int lo = 0, hi = p.batch;
-        while (hi - lo > 1) {
-          const int mid = (lo + hi) >> 1;
-          if (static_cast<long long>(s_prefix[mid]) * Hkv <= x) lo = mid; else hi = mid;
+    if (lane != 0) return;
+    tma_prefetch_desc(&map_k);
+    tma_prefetch_desc(&map_v);
+    tma_prefetch_desc(&map_k16);
+    tma_prefetch_desc(&map_v16);
+    int it = 0, segc = 0;
+    bool ok = true;
+    int piece = cta;   // the CTA's own static piece first, then tickets
+    long long r_begin = pc.start(piece), r_end = pc.start(piece + 1);
+    SegDesc cur = dec_locate(s_prefix, p.batch, Hkv, r_begin, r_begin, r_end, piece);
+    // metadata of a segment, fetched one segment ahead: its length and its first two block ids
+    int cur_len = p.context_lens[cur.seq];
+    const int* cur_bt = p.block_tables + cur.seq * p.bt_row_stride;
+    int cur_col0 = (cur.t0 * kTile) / p.block_size;
+    int cur_blk0 = cur_bt[cur_col0];
+    int cur_blk1 = cur_col0 + 1 < p.bt_cols ? cur_bt[cur_col0 + 1] : -1;
+    while (true) {
+      cur_len = cur_len > max_len ? max_len : cur_len;
+      cur.len = cur_len;
+      const int last_col = (cur_len - 1) / p.block_size;
+      int col_now = cur_col0;
+      long long blk_now = cur_blk0;
+      long long blk_next = cur_col0 < last_col ? cur_blk1 : -1;
+      SegDesc nxt;
+      nxt.seq = -1;
+      int nxt_len = 0, nxt_col0 = 0, nxt_blk0 = -1, nxt_blk1 = -1;
+      const int* nxt_bt = nullptr;
+      for (int t = cur.t0; t < cur.t1; ++t, ++it) {
+        const int stage = it % kDecStages;
+        const uint32_t ph = (it / kDecStages) & 1;
+        if (!mbar_wait(&bar_empty[stage], ph ^ 1, abort_flag)) { ok = false; break; }
+        const int tok0 = t * kTile;
+        const int col = tok0 / p.block_size;
+        if (col != col_now) {
+          col_now = col;
+          blk_now = blk_next;
+          blk_next = col_now < last_col ? cur_bt[col_now + 1] : -1;
         }
-        const int seq = lo;
-        const int nt = s_prefix[seq + 1] - s_prefix[seq];
-        const long long rem = x - static_cast<long long>(s_prefix[seq]) * Hkv;
-        const int h = static_cast<int>(rem / nt);
-        const int t0 = static_cast<int>(rem - static_cast<long long>(h) * nt);
-        const long long seg_end = x - t0 + nt;
-        const long long my_end = seg_end < r_end ? seg_end : r_end;
-        const int t1 = t0 + static_cast<int>(my_end - x);
-        const int* bt_row = p.block_tables + seq * p.bt_row_stride;
-        int cur_col = -1;
-        long long cur_block = -1;
-        for (int t = t0; t < t1; ++t, ++it) {
-          const int stage = it % kDecStages;
-          const uint32_t ph = (it / kDecStages) & 1;
-          if (!mbar_wait(&bar_empty[stage], ph ^ 1, abort_flag)) { ok = false; break; }
-          const int tok0 = t * kTile;
-          const int col = tok0 / p.block_size;
-          if (col != cur_col) { cur_col = col; cur_block = bt_row[col]; }
-          int slot0 = -kTile;  // out-of-range block id: the box lies outside the tensor and reads zeros
-          if (cur_block >= 0 && cur_block < p.num_blocks)
-            slot0 = static_cast<int>(cur_block * p.block_size + (tok0 - col * p.block_size));
-          unsigned char* st = stages + stage * kStageBytes;
-          mbar_expect_tx(&bar_full[stage], kStageBytes);
-          tma_load_3d(st, &map_k, &bar_full[stage], 0, h, slot0);
-          tma_load_3d(st + kSubTileBytes, &map_k, &bar_full[stage], 64, h, slot0);
-          tma_load_3d(st + 2 * kSubTileBytes, &map_v, &bar_full[stage], 0, h, slot0);
-          tma_load_3d(st + 3 * kSubTileBytes, &map_v, &bar_full[stage], 64, h, slot0);
+        int slot0 = -kTile;  // out-of-range block id: the box lies outside the tensor and reads zeros
+        if (blk_now >= 0 && blk_now < p.num_blocks)
+          slot0 = static_cast<int>(blk_now * p.block_size + (tok0 - col * p.block_size));
+        unsigned char* st = stages + stage * kStageBytes;
+        const int valid = cur_len - tok0;
+        const int nslab = valid >= kTile - 15 ? 4 : (valid + 15) >> 4;
+        uint32_t tx = nslab == 4 ? kStageBytes : nslab * 4 * 2048;
+        const bool first = t == cur.t0;
+        if (first) {
+          // descriptor and query rows travel with the segment's first tile
+          s_desc[segc % kSegRing] = cur;
+          tx += G * 256;
         }
-        x = my_end;
+        mbar_expect_tx(&bar_full[stage], tx);
+        if (first)
+          bulk_load_1d(s_q + (segc % kSegRing) * G * 128,
+                       p.q + cur.seq * p.q_row_stride + static_cast<long long>(cur.h) * G * 128, G * 256, &bar_full[stage]);
+        if (nslab == 4) {
+          tma_load_3d(st, &map_k, &bar_full[stage], 0, cur.h, slot0);
+          tma_load_3d(st + kSubTileBytes, &map_k, &bar_full[stage], 64, cur.h, slot0);
+          tma_load_3d(st + 2 * kSubTileBytes, &map_v, &bar_full[stage], 0, cur.h, slot0);
+          tma_load_3d(st + 3 * kSubTileBytes, &map_v, &bar_full[stage], 64, cur.h, slot0);
+        } else {
+          // ragged last tile of the sequence: fetch only the 16-token slabs that hold tokens
+          for (int sl = 0; sl < nslab; ++sl) {
+            unsigned char* d = st + sl * 2048;
+            tma_load_3d(d, &map_k16, &bar_full[stage], 0, cur.h, slot0 + sl * 16);
+            tma_load_3d(d + kSubTileBytes, &map_k16, &bar_full[stage], 64, cur.h, slot0 + sl * 16);
+            tma_load_3d(d + 2 * kSubTileBytes, &map_v16, &bar_full[stage], 0, cur.h, slot0 + sl * 16);
+            tma_load_3d(d + 3 * kSubTileBytes, &map_v16, &bar_full[stage], 64, cur.h, slot0 + sl * 16);
+          }
+        }
+        if (first) {
+          // with this segment under way, find the next one and start fetching its metadata
+          long long x = cur.seg_start + cur.t1;   // flat position after this segment's part
+          if (x >= r_end) {
+            // next piece: a ticket.  Each of the g CTAs draws until it fails, so exactly
+            // dynamic() + g tickets are drawn per launch; whoever draws the last one resets the counter.
+            int np = -1;
+            if (pc.dynamic() > 0) {
+              const unsigned int tk = atomicAdd(p.ticket, 1u);
+              if (tk == static_cast<unsigned int>(pc.dynamic() + pc.g - 1)) atomicExch(p.ticket, 0u);
+              if (tk < static_cast<unsigned int>(pc.dynamic())) np = pc.g + static_cast<int>(tk);
+            }
+            if (np >= 0) {
+              piece = np;
+              r_begin = pc.start(np);
+              r_end = pc.start(np + 1);
+              x = r_begin;
+            } else {
+              x = -1;
+            }
+          }
+          if (x >= 0) {
+            nxt = dec_locate(s_prefix, p.batch, Hkv, x, r_begin, r_end, piece);
+            nxt_len = p.context_lens[nxt.seq];
+            nxt_bt = p.block_tables + nxt.seq * p.bt_row_stride;
+            nxt_col0 = (nxt.t0 * kTile) / p.block_size;
+            nxt_blk0 = nxt_bt[nxt_col0];
+            nxt_blk1 = nxt_col0 + 1 < p.bt_cols ? nxt_bt[nxt_col0 + 1] : -1;
+          }
+        }
       }
-      if (!ok) {
-        // unwind: give loads already issued a bounded chance to land before the CTA exits
-        atomicExch(&g_status_decode, 1);
+      if (!ok) break;
+      ++segc;
+      if (nxt.seq < 0) break;
+      cur = nxt;
+      cur_len = nxt_len;
+      cur_bt = nxt_bt;
+      cur_col0 = nxt_col0;
+      cur_blk0 = nxt_blk0;
+      cur_blk1 = nxt_blk1;
+    }
+    if (ok) {
+      // end marker: a descriptor with seq = -1 on the next full-barrier, no bytes attached
+      const int stage = it % kDecStages;
+      const uint32_t ph = (it / kDecStages) & 1;
+      if (mbar_wait(&bar_empty[stage], ph ^ 1, abort_flag)) {
+        s_desc[segc % kSegRing].seq = -1;
+        mbar_arrive(&bar_full[stage]);
+      }
+    } else {
+      atomicExch(&g_status_decode, 1);
+    }
+    return;
+  }
+
+  if (warp == kDecEpilogueWarp) {
+    // =========================== epilogue warp ===========================
+    // Lane owns 4 of the 128 output dims.  Step 1 for every segment: combine the four consumer
+    // warps' states and store the row (or the partial) -- no waiting on global memory, so the
+    // consumers get their hand-off buffer back at once.  The slow part of a partial (fence, arrival
+    // counter, merge: several dependent trips to L2) is queued and flushed when no hand-off is
+    // waiting; one fence and one round of atomics then serve every queued partial.
+    int n_pending = 0;
+    auto flush = [&]() {
+      if (n_pending == 0) return;
+      __threadfence();
+      __syncwarp();
+      int expected = 0, old = -1;
+      if (lane < n_pending) {
+        const SegDesc& d = s_pending[lane];
+        expected = pc.of(d.seg_start + d.nt - 1) - pc.of(d.seg_start);
+        old = atomicAdd(&p.counters[d.seq * Hkv + d.h], 1);
+      }
+      const unsigned last_mask = __ballot_sync(0xffffffffu, lane < n_pending && old == expected);
+      if (last_mask) __threadfence();
+      for (int k = 0; k < n_pending; ++k) {
+        if (!((last_mask >> k) & 1u)) continue;
+        // this CTA brought the last partial of (sequence, head) k: merge them all
+        const SegDesc d = s_pending[k];
+        const int i_first = pc.of(d.seg_start);
+        const int n = pc.of(d.seg_start + d.nt - 1) - i_first + 1;
+        for (int gq = 0; gq < G; ++gq) {
+          float M = -INFINITY, L = 0.f;
+          float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+          for (int base = 0; base < n; base += 32) {
+            const int cnt = n - base < 32 ? n - base : 32;
+            // lane j looks after partial base + j: its slot, its (max, sum)
+            int sl = 0;
+            float mj = -INFINITY, lj = 0.f;
+            if (lane < cnt) {
+              const int i = i_first + base + lane;
+              sl = i * 2 + (d.seg_start <= pc.start(i) ? 0 : 1);
+              const float2 v = __ldcg(reinterpret_cast<const float2*>(p.ws_ml + (sl * G + gq) * 2));
+              mj = v.x;
+              lj = v.y;
+            }
+            float Mr = mj;
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) Mr = fmaxf(Mr, __shfl_xor_sync(0xffffffffu, Mr, off));
+            const float Mn = fmaxf(M, Mr);
+            const float rescale = fast_exp2(M - Mn);
+            const float wj = fast_exp2(mj - Mn);
+            float Lr = lj * wj;
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) Lr += __shfl_xor_sync(0xffffffffu, Lr, off);
+            L = L * rescale + Lr;
+            acc.x *= rescale; acc.y *= rescale; acc.z *= rescale; acc.w *= rescale;
+            M = Mn;
+            // every lane accumulates its 4 dims over the partials, 8 independent loads at a time
+            for (int u0 = 0; u0 < cnt; u0 += 8) {
+              float4 v[8];
+#pragma unroll
+              for (int u = 0; u < 8; ++u) {
+                const int slu = __shfl_sync(0xffffffffu, sl, (u0 + u) & 31);
+                if (u0 + u < cnt)
+                  v[u] = __ldcg(reinterpret_cast<const float4*>(p.ws_o + (static_cast<long long>(slu) * G + gq) * 128 + lane * 4));
+              }
+#pragma unroll
+              for (int u = 0; u < 8; ++u) {
+                const float wu = __shfl_sync(0xffffffffu, wj, (u0 + u) & 31);
+                if (u0 + u < cnt) { acc.x += v[u].x * wu; acc.y += v[u].y * wu; acc.z += v[u].z * wu; acc.w += v[u].w * wu; }
+              }
+            }
+          }
+          const float inv = 1.f / L;
+          uint2 o2;
+          o2.x = pack_bf16(acc.x * inv, acc.y * inv);
+          o2.y = pack_bf16(acc.z * inv, acc.w * inv);
+          *reinterpret_cast<uint2*>(p.out + (static_cast<long long>(d.seq) * p.H + d.h * G + gq) * 128 + lane * 4) = o2;
+        }
+        if (lane == 0) p.counters[d.seq * Hkv + d.h] = 0;
+      }
+      __syncwarp();
+      n_pending = 0;
+    };
+    bool ok = true;
+    for (int n = 0;; ++n) {
+      const int e = n % p.n_merge;
+      const uint32_t ph = (n / p.n_merge) & 1;
+      if (!mbar_try_wait(&bar_merge_full[e], ph)) {
+        flush();                                   // nothing to combine right now: do the slow part
+        if (!mbar_wait(&bar_merge_full[e], ph, abort_flag)) { ok = false; break; }
+      }
+      const SegDesc d = s_merge_desc[e];
+      if (d.seq < 0) break;
+      const float* mo = merge_o + e * kDecConsumerWarps * G * 128;
+      const float* ml = merge_ml + e * kDecConsumerWarps * G * 2;
+      const bool full = d.t0 == 0 && d.t1 == d.nt;
+      for (int gq = 0; gq < G; ++gq) {
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < kDecConsumerWarps; ++w) M = fmaxf(M, ml[(w * G + gq) * 2]);
+        float L = 0.f;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int w = 0; w < kDecConsumerWarps; ++w) {
+          const float wgt = fast_exp2(ml[(w * G + gq) * 2] - M);
+          L += ml[(w * G + gq) * 2 + 1] * wgt;
+          const float4 v = *reinterpret_cast<const float4*>(mo + (w * G + gq) * 128 + lane * 4);
+          acc.x += v.x * wgt; acc.y += v.y * wgt; acc.z += v.z * wgt; acc.w += v.w * wgt;
+        }
+        if (full) {
+          const float inv = 1.f / L;
+          uint2 o2;
+          o2.x = pack_bf16(acc.x * inv, acc.y * inv);
+          o2.y = pack_bf16(acc.z * inv, acc.w * inv);
+          *reinterpret_cast<uint2*>(p.out + (static_cast<long long>(d.seq) * p.H + d.h * G + gq) * 128 + lane * 4) = o2;
+        } else {
+          *reinterpret_cast<float4*>(p.ws_o + (static_cast<long long>(d.slot) * G + gq) * 128 + lane * 4) = acc;
+          if (lane == 0) *reinterpret_cast<float2*>(p.ws_ml + (d.slot * G + gq) * 2) = make_float2(M, L);
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bar_merge_empty[e]);   // the consumers may refill the hand-off buffer
+      if (!full) {
+        if (lane == 0) s_pending[n_pending] = d;
+        __syncwarp();
+        if (++n_pending == kDecPending) flush();
       }
     }
+    if (ok) flush();
+    if (lane == 0) DEC_TRACE(4);
     return;
   }
 
@@ -197,40 +528,28 @@ decode_attn_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap map
   const int row = lane >> 2;        // A/C fragment row (query head within the kv group)
   const int quad = lane & 3;
   const bool row0_ok = row < G, row1_ok = row + 8 < G;
-  int it = 0;
-  long long x = r_begin;
+  int it = 0, segc = 0;
   bool ok = true;
-  while (x < r_end && ok) {
-    int lo = 0, hi = p.batch;
-    while (hi - lo > 1) {
-      const int mid = (lo + hi) >> 1;
-      if (static_cast<long long>(s_prefix[mid]) * Hkv <= x) lo = mid; else hi = mid;
-    }
-    const int seq = lo;
-    const int nt = s_prefix[seq + 1] - s_prefix[seq];
-    const long long seg_start_seq = static_cast<long long>(s_prefix[seq]) * Hkv;
-    const long long rem = x - seg_start_seq;
-    const int h = static_cast<int>(rem / nt);
-    const int t0 = static_cast<int>(rem - static_cast<long long>(h) * nt);
-    const long long seg_start = x - t0;
-    const long long seg_end = seg_start + nt;
-    const long long my_end = seg_end < r_end ? seg_end : r_end;
-    const int t1 = t0 + static_cast<int>(my_end - x);
-    int len = p.context_lens[seq];
-    len = len > max_len ? max_len : len;
-
-    // query fragments: rows = the G heads sharing kv head h
-    uint32_t qa[8][4];
+  while (ok) {
+    // ---- a new segment: its descriptor and query rows arrive with its first tile ----
     {
-      const __nv_bfloat16* qb = p.q + seq * p.q_row_stride + static_cast<long long>(h) * G * 128;
-      const uint32_t* q0 = reinterpret_cast<const uint32_t*>(qb + row * 128);
-      const uint32_t* q1 = reinterpret_cast<const uint32_t*>(qb + (row + 8) * 128);
+      const int stage = it % kDecStages;
+      const uint32_t ph = (it / kDecStages) & 1;
+      if (!mbar_wait(&bar_full[stage], ph, abort_flag)) { ok = false; break; }
+    }
+    const SegDesc d = s_desc[segc % kSegRing];
+    if (d.seq < 0) break;
+    if (tid == 0 && it == 0) DEC_TRACE(2);
+    uint32_t qa[8][4];   // query fragments: rows = the G heads sharing the kv head
+    {
+      const uint32_t* q0 = reinterpret_cast<const uint32_t*>(s_q + (segc % kSegRing) * G * 128 + row * 128);
+      const uint32_t* q1 = q0 + 8 * 64;
 #pragma unroll
       for (int ks = 0; ks < 8; ++ks) {
-        qa[ks][0] = row0_ok ? __ldg(q0 + ks * 8 + quad) : 0u;
-        qa[ks][1] = row1_ok ? __ldg(q1 + ks * 8 + quad) : 0u;
-        qa[ks][2] = row0_ok ? __ldg(q0 + ks * 8 + 4 + quad) : 0u;
-        qa[ks][3] = row1_ok ? __ldg(q1 + ks * 8 + 4 + quad) : 0u;
+        qa[ks][0] = row0_ok ? q0[ks * 8 + quad] : 0u;
+        qa[ks][1] = row1_ok ? q1[ks * 8 + quad] : 0u;
+        qa[ks][2] = row0_ok ? q0[ks * 8 + 4 + quad] : 0u;
+        qa[ks][3] = row1_ok ? q1[ks * 8 + 4 + quad] : 0u;
       }
     }
     float o[16][4];
@@ -238,11 +557,11 @@ decode_attn_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap map
     for (int n = 0; n < 16; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
 
-    for (int t = t0; t < t1; ++t, ++it) {
+    for (int t = d.t0; t < d.t1; ++t, ++it) {
       const int stage = it % kDecStages;
       const uint32_t ph = (it / kDecStages) & 1;
-      if (!mbar_wait(&bar_full[stage], ph, abort_flag)) { ok = false; break; }
-      const int valid = len - (t * kTile + warp * 16);  // valid tokens in this warp's 16-token slab
+      if (t != d.t0 && !mbar_wait(&bar_full[stage], ph, abort_flag)) { ok = false; break; }
+      const int valid = d.len - (t * kTile + warp * 16);  // valid tokens in this warp's 16-token slab
       if (valid > 0) {
         const uint32_t st = smem_u32(stages + stage * kStageBytes);
         const uint32_t k_base = st, v_base = st + 2 * kSubTileBytes;
@@ -334,84 +653,55 @@ decode_attn_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap map
     }
     if (!ok) break;
 
-    // ---- combine the four warps, then either finish the (sequence, head) or leave a partial ----
+    // ---- hand the warp's running state to the epilogue warp and move on ----
     l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
     l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
     {
-      float* mo = merge_o + warp * G * 128;
+      const int e = segc % p.n_merge;
+      const uint32_t ph = (segc / p.n_merge) & 1;
+      if (!mbar_wait(&bar_merge_empty[e], ph ^ 1, abort_flag)) { ok = false; break; }
+      float* mo = merge_o + (e * kDecConsumerWarps + warp) * G * 128;
 #pragma unroll
       for (int n = 0; n < 16; ++n) {
         if (row0_ok) *reinterpret_cast<float2*>(mo + row * 128 + n * 8 + quad * 2) = make_float2(o[n][0], o[n][1]);
         if (row1_ok) *reinterpret_cast<float2*>(mo + (row + 8) * 128 + n * 8 + quad * 2) = make_float2(o[n][2], o[n][3]);
       }
       if (quad == 0) {
-        float* ml = merge_ml + warp * G * 2;
+        float* ml = merge_ml + (e * kDecConsumerWarps + warp) * G * 2;
         if (row0_ok) { ml[row * 2] = m0; ml[row * 2 + 1] = l0; }
         if (row1_ok) { ml[(row + 8) * 2] = m1; ml[(row + 8) * 2 + 1] = l1; }
       }
+      if (tid == 0) s_merge_desc[e] = d;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bar_merge_full[e]);
     }
-    named_bar_sync(1, kDecConsumers);
-    const bool full = (x == seg_start) && (my_end == seg_end);
-    const int slot = static_cast<int>(cta) * 2 + (seg_start <= r_begin ? 0 : 1);
-    for (int g = 0; g < G; ++g) {
-      float M = -INFINITY;
-#pragma unroll
-      for (int w = 0; w < kDecConsumerWarps; ++w) M = fmaxf(M, merge_ml[(w * G + g) * 2]);
-      float L = 0.f, acc = 0.f;
-#pragma unroll
-      for (int w = 0; w < kDecConsumerWarps; ++w) {
-        const float wgt = fast_exp2(merge_ml[(w * G + g) * 2] - M);
-        L += merge_ml[(w * G + g) * 2 + 1] * wgt;
-        acc += merge_o[(w * G + g) * 128 + tid] * wgt;
-      }
-      if (full) {
-        p.out[(static_cast<long long>(seq) * p.H + h * G + g) * 128 + tid] = __float2bfloat16(acc / L);
-      } else {
-        p.ws_o[(static_cast<long long>(slot) * G + g) * 128 + tid] = acc;
-        if (tid == 0) {
-          p.ws_ml[(slot * G + g) * 2] = M;
-          p.ws_ml[(slot * G + g) * 2 + 1] = L;
-        }
-      }
-    }
-    if (!full) {
-      // last-arriver merge across the CTAs that share this (sequence, head)
-      const long long c_first = ((seg_start + 1) * grid_eff - 1) / T;
-      const long long c_last = (seg_end * grid_eff - 1) / T;
-      __threadfence();
-      named_bar_sync(1, kDecConsumers);
-      if (tid == 0) {
-        const int old = atomicAdd(&p.counters[seq * Hkv + h], 1);
-        s_last = (old == static_cast<int>(c_last - c_first));
-      }
-      named_bar_sync(1, kDecConsumers);
-      if (s_last) {
-        __threadfence();
-        for (int g = 0; g < G; ++g) {
-          float M = -INFINITY, L = 0.f, acc = 0.f;
-          for (long long c = c_first; c <= c_last; ++c) {
-            const long long cb = c * T / grid_eff;
-            const int sl = static_cast<int>(c) * 2 + (seg_start <= cb ? 0 : 1);
-            const float2 ml = ld_cg_f32x2(p.ws_ml + (sl * G + g) * 2);
-            const float ov = ld_cg_f32(p.ws_o + (static_cast<long long>(sl) * G + g) * 128 + tid);
-            const float Mn = fmaxf(M, ml.x);
-            const float wa = fast_exp2(M - Mn), wb = fast_exp2(ml.x - Mn);
-            L = L * wa + ml.y * wb;
-            acc = acc * wa + ov * wb;
-            M = Mn;
-          }
-          p.out[(static_cast<long long>(seq) * p.H + h * G + g) * 128 + tid] = __float2bfloat16(acc / L);
-        }
-        if (tid == 0) p.counters[seq * Hkv + h] = 0;
-      }
-    }
-    named_bar_sync(1, kDecConsumers);  // merge buffers are reused by the next segment
-    x = my_end;
+    ++segc;
   }
-  if (!ok && lane == 0) atomicExch(&g_status_decode, 1);
+  if (tid == 0) DEC_TRACE(3);
+#ifdef B200_TRACE
+  if (tid == 0) { g_dec_trace[blockIdx.x * 8 + 5] = segc; g_dec_trace[blockIdx.x * 8 + 6] = it; }
+#endif
+  // tell the epilogue warp that nothing more will come
+  if (ok) {
+    const int e = segc % p.n_merge;
+    const uint32_t ph = (segc / p.n_merge) & 1;
+    if (mbar_wait(&bar_merge_empty[e], ph ^ 1, abort_flag)) {
+      if (tid == 0) s_merge_desc[e].seq = -1;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bar_merge_full[e]);
+    }
+  } else if (lane == 0) {
+    atomicExch(&g_status_decode, 1);
+  }
 }
+
+#ifdef B200_TRACE
+extern "C" int b200_debug_trace(unsigned long long* host_out, int n) {
+  return static_cast<int>(cudaMemcpyFromSymbol(host_out, g_dec_trace, sizeof(unsigned long long) * n));
+}
+#endif
 
 int read_status_decode() {
   int v = 0;
@@ -419,14 +709,22 @@ int read_status_decode() {
   return v;
 }
 
+// Two hand-off buffers between consumers and the epilogue warp when two CTAs still fit on an SM with them.
+static int decode_merge_buffers(int G) { return G <= 2 ? 2 : 1; }
+
 static size_t decode_smem_bytes(int G) {
-  return 1024 + static_cast<size_t>(kDecStages) * kStageBytes + static_cast<size_t>(kDecConsumerWarps) * G * 130 * 4 +
-         (kDecMaxBatch + 1) * 4 + 64;
+  return 1024 + static_cast<size_t>(kDecStages) * kStageBytes + static_cast<size_t>(kSegRing) * G * 256 +
+         static_cast<size_t>(decode_merge_buffers(G)) * kDecConsumerWarps * G * 130 * 4 + (kDecMaxBatch + 1) * 4 + 64;
 }
 
 static int decode_grid() { return 2 * sm_count(); }
 
-static long long decode_partial_bytes(int grid) { return static_cast<long long>(grid) * 2 * kMaxG * 130 * 4; }
+// Two partial slots per piece; at most grid static + grid big + 4 * grid small pieces.
+static long long decode_partial_slots(int grid) { return 12LL * grid; }
+static long long decode_partial_bytes(int grid, int G) { return decode_partial_slots(grid) * G * 130 * 4; }
+static long long decode_ws_bytes(int grid, int G) {
+  return kWsStatusBytes + static_cast<long long>(kWsCounterInts) * 4 + decode_partial_bytes(grid, G);
+}
 
 }  // namespace b200
 
@@ -438,8 +736,9 @@ extern "C" int64_t b200_decode_workspace_bytes(int32_t max_batch, int32_t num_he
                      num_heads, num_kv_heads, head_dim);
   const int grid = decode_grid();
   if (grid <= 0) return set_error(kErrNoDriver, "decode_workspace_bytes: no CUDA device");
-  const long long per_launch = max_batch < kDecMaxBatch ? max_batch : kDecMaxBatch;
-  return kWsStatusBytes + decode_partial_bytes(grid) + per_launch * num_kv_heads * 4;
+  if (num_kv_heads > 128 || num_heads / num_kv_heads > kMaxG)
+    return set_error(kErrBadShape, "decode_workspace_bytes: at most 128 kv heads and %d query heads per kv head", kMaxG);
+  return decode_ws_bytes(grid, num_heads / num_kv_heads);
 }
 
 extern "C" int b200_decode_attn(const void* q, int64_t q_row_stride, const void* k_cache, const void* v_cache,
@@ -458,6 +757,7 @@ extern "C" int b200_decode_attn(const void* q, int64_t q_row_stride, const void*
                      num_heads, num_kv_heads);
   const int G = num_heads / num_kv_heads;
   if (G > kMaxG) return set_error(kErrBadShape, "decode_attn: at most %d query heads per kv head (got %d)", kMaxG, G);
+  if (num_kv_heads > 128) return set_error(kErrBadShape, "decode_attn: at most 128 kv heads (got %d)", num_kv_heads);
   if (block_size <= 0 || block_size % 256)
     return set_error(kErrBadShape, "decode_attn: block_size must be a positive multiple of 256 (got %d)", block_size);
   if (num_blocks <= 0 || num_blocks * block_size >= (1LL << 31))
@@ -472,8 +772,7 @@ extern "C" int b200_decode_attn(const void* q, int64_t q_row_stride, const void*
     return set_error(kErrMisaligned, "decode_attn: q, caches and out must be 16-byte aligned");
   const int grid = decode_grid();
   if (grid <= 0) return set_error(kErrNoDriver, "decode_attn: no CUDA device");
-  const long long per_launch = batch < kDecMaxBatch ? batch : kDecMaxBatch;
-  const long long need = kWsStatusBytes + decode_partial_bytes(grid) + per_launch * num_kv_heads * 4;
+  const long long need = decode_ws_bytes(grid, G);
   if (!workspace || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 15))
     return set_error(kErrWorkspace, "decode_attn: workspace of %lld bytes (16-byte aligned, zero-filled once) required, got %lld",
                      need, (long long)workspace_bytes);
@@ -484,6 +783,13 @@ extern "C" int b200_decode_attn(const void* q, int64_t q_row_stride, const void*
   if (rc) return rc;
   rc = make_tokens_heads_map(&map_v, v_cache, static_cast<uint64_t>(num_blocks) * block_size, num_kv_heads,
                              static_cast<uint64_t>(num_kv_heads) * 128, kTile);
+  if (rc) return rc;
+  CUtensorMap map_k16, map_v16;   // 16-token boxes for the ragged last tile of a sequence
+  rc = make_tokens_heads_map(&map_k16, k_cache, static_cast<uint64_t>(num_blocks) * block_size, num_kv_heads,
+                             static_cast<uint64_t>(num_kv_heads) * 128, 16);
+  if (rc) return rc;
+  rc = make_tokens_heads_map(&map_v16, v_cache, static_cast<uint64_t>(num_blocks) * block_size, num_kv_heads,
+                             static_cast<uint64_t>(num_kv_heads) * 128, 16);
   if (rc) return rc;
 
   const size_t smem = decode_smem_bytes(G);
@@ -505,9 +811,22 @@ extern "C" int b200_decode_attn(const void* q, int64_t q_row_stride, const void*
   p.block_size = block_size;
   p.num_blocks = num_blocks;
   p.scale_log2 = scale * 1.4426950408889634f;
-  p.ws_o = reinterpret_cast<float*>(ws + kWsStatusBytes);
-  p.ws_ml = p.ws_o + static_cast<long long>(grid) * 2 * kMaxG * 128;
-  p.counters = reinterpret_cast<int*>(ws + kWsStatusBytes + decode_partial_bytes(grid));
+  p.n_merge = decode_merge_buffers(G);
+  {
+    auto env_int = [](const char* name, int dflt) { const char* e = getenv(name); return e ? atoi(e) : dflt; };
+    static const int dyn = env_int("B200_DECODE_DYN_FACTOR", 256);
+    static const int big = env_int("B200_DECODE_BIG_PCT", 15);
+    static const int small = env_int("B200_DECODE_SMALL_PCT100", 375);
+    static const int small_n = env_int("B200_DECODE_SMALL_N", 4);
+    p.dyn_factor = dyn;
+    p.big_pct = big;
+    p.small_pct100 = small;
+    p.small_n = small_n < 1 ? 1 : (small_n > 4 ? 4 : small_n);
+  }
+  p.ticket = reinterpret_cast<unsigned int*>(ws);
+  p.counters = reinterpret_cast<int*>(ws + kWsStatusBytes);
+  p.ws_o = reinterpret_cast<float*>(ws + kWsStatusBytes + static_cast<long long>(kWsCounterInts) * 4);
+  p.ws_ml = p.ws_o + decode_partial_slots(grid) * G * 128;
   p.q_row_stride = q_row_stride;
   for (int b0 = 0; b0 < batch; b0 += kDecMaxBatch) {
     p.batch = batch - b0 < kDecMaxBatch ? batch - b0 : kDecMaxBatch;
@@ -515,7 +834,7 @@ extern "C" int b200_decode_attn(const void* q, int64_t q_row_stride, const void*
     p.out = static_cast<__nv_bfloat16*>(out) + static_cast<long long>(b0) * num_heads * 128;
     p.context_lens = context_lens + b0;
     p.block_tables = block_tables + b0 * bt_row_stride;
-    decode_attn_kernel<<<grid, kDecThreads, smem, static_cast<cudaStream_t>(stream)>>>(p, map_k, map_v);
+    decode_attn_kernel<<<grid, kDecThreads, smem, static_cast<cudaStream_t>(stream)>>>(p, map_k, map_v, map_k16, map_v16);
     g_launches.fetch_add(1);
     rc = check_cuda(cudaGetLastError(), "decode_attn launch");
     if (rc) return rc;
@@ -535,10 +854,9 @@ extern "C" int b200_decode_attn(const void* q, int64_t q_row_stride, const void*
 // ---------------------------------------------------------------------------------------------
 namespace b200 {
 
-constexpr int kStaticMaxGrid = 320;        // persistent CTAs the static scratch has partial slots for
-constexpr int kStaticMaxCounters = 8192;   // (sequence, kv head) pairs per launch: min(batch, 1024) * Hkv
+constexpr int kStaticMaxGridTimesG = 320 * 4;   // persistent CTAs x query heads per kv head the scratch has room for
 constexpr long long kStaticScratchBytes =
-    kWsStatusBytes + static_cast<long long>(kStaticMaxGrid) * 2 * kMaxG * 130 * 4 + kStaticMaxCounters * 4;
+    kWsStatusBytes + static_cast<long long>(kWsCounterInts) * 4 + 12LL * kStaticMaxGridTimesG * 130 * 4;
 
 static __device__ __align__(256) unsigned char g_decode_static_scratch[kStaticScratchBytes];
 
@@ -581,25 +899,21 @@ extern "C" int b200_decode_attn_static(const void* q, int64_t q_row_stride, cons
                      num_heads, num_kv_heads);
   const int grid = decode_grid();
   if (grid <= 0) return set_error(kErrNoDriver, "decode_attn_static: no CUDA device");
-  if (grid > kStaticMaxGrid)
+  const int G = num_heads / num_kv_heads;
+  if (static_cast<long long>(grid) * G > kStaticMaxGridTimesG || num_kv_heads > 128)
     return set_error(kErrWorkspace,
-                     "decode_attn_static: this GPU runs %d persistent CTAs but the built-in scratch has room for %d; "
-                     "use b200_decode_attn with a caller-owned workspace", grid, kStaticMaxGrid);
-  const long long per_launch = batch < kDecMaxBatch ? batch : kDecMaxBatch;
-  if (per_launch * num_kv_heads > kStaticMaxCounters)
-    return set_error(kErrWorkspace,
-                     "decode_attn_static: min(batch, %d) * num_kv_heads = %lld exceeds the built-in scratch's limit of %d; "
-                     "use b200_decode_attn with a caller-owned workspace", kDecMaxBatch, per_launch * num_kv_heads,
-                     kStaticMaxCounters);
+                     "decode_attn_static: %d persistent CTAs x %d query heads per kv head exceeds the built-in scratch's "
+                     "limit of %d (and kv heads must be <= 128); use b200_decode_attn with a caller-owned workspace",
+                     grid, G, kStaticMaxGridTimesG);
   void* scratch = nullptr;
   int rc = static_scratch_address(&scratch);
   if (rc) return rc;
   // The array keeps whatever the previous call left.  Partials are always written before they are
-  // read; the arrival counters are the one part that must start at zero, so clear them here.
-  unsigned char* counters = static_cast<unsigned char*>(scratch) + kWsStatusBytes + decode_partial_bytes(grid);
-  rc = check_cuda(cudaMemsetAsync(counters, 0, static_cast<size_t>(per_launch) * num_kv_heads * 4,
+  // read; the ticket counter and the arrival counters are what must start at zero, so clear them here.
+  const long long per_launch = batch < kDecMaxBatch ? batch : kDecMaxBatch;
+  rc = check_cuda(cudaMemsetAsync(scratch, 0, kWsStatusBytes + static_cast<size_t>(per_launch) * num_kv_heads * 4,
                                   static_cast<cudaStream_t>(stream)),
-                  "decode_attn_static: clearing the arrival counters");
+                  "decode_attn_static: clearing the counters");
   if (rc) return rc;
   return b200_decode_attn(q, q_row_stride, k_cache, v_cache, num_blocks, block_size, block_tables, bt_row_stride, bt_cols,
                           context_lens, out, scratch, kStaticScratchBytes, batch, num_heads, num_kv_heads, head_dim,

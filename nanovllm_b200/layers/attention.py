@@ -19,7 +19,7 @@ from ..utils import context as _own_context
 # reference engine's get_context when the layer is installed into nano-vllm.
 _context_getter = _own_context.get_context
 
-_DECODE_WS_BATCH = 1024  # the library splits larger batches into launches of at most this many
+_DECODE_WS_BATCH = 512  # the library splits larger batches into launches of at most this many
 
 
 def get_context():
@@ -65,9 +65,10 @@ _workspaces: dict = {}
 
 
 def _decode_workspace(device, num_heads, num_kv_heads, head_dim):
-    """One zero-initialised workspace per (device, kv heads); layers run back to back on a stream
-    and share it.  Allocated on first use (the engine's eager warm-up precedes graph capture)."""
-    key = (device.index, num_kv_heads)
+    """One zero-initialised workspace per (device, query heads per kv head); layers run back to back
+    on a stream and share it.  Allocated on first use (the engine's eager warm-up precedes graph
+    capture)."""
+    key = (device.index, num_heads // num_kv_heads)
     ws = _workspaces.get(key)
     if ws is None:
         lib = _lib.load()
