@@ -211,6 +211,11 @@ decode_attn_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap map
     mbar_fence_init();
   }
 
+  // Launched with programmatic stream serialization: everything above overlapped the tail of
+  // the previous kernel in the stream (store_kvcache); nothing below may run before that kernel
+  // has finished and its writes are visible.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+
   // ---- tile counts per sequence and their exclusive prefix (block scan) ----
   {
     const int per = (p.batch + kDecThreads - 1) / kDecThreads;
@@ -834,9 +839,19 @@ extern "C" int b200_decode_attn(const void* q, int64_t q_row_stride, const void*
     p.out = static_cast<__nv_bfloat16*>(out) + static_cast<long long>(b0) * num_heads * 128;
     p.context_lens = context_lens + b0;
     p.block_tables = block_tables + b0 * bt_row_stride;
-    decode_attn_kernel<<<grid, kDecThreads, smem, static_cast<cudaStream_t>(stream)>>>(p, map_k, map_v, map_k16, map_v16);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(kDecThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = static_cast<cudaStream_t>(stream);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const cudaError_t le = cudaLaunchKernelEx(&cfg, decode_attn_kernel, p, map_k, map_v, map_k16, map_v16);
     g_launches.fetch_add(1);
-    rc = check_cuda(cudaGetLastError(), "decode_attn launch");
+    rc = check_cuda(le != cudaSuccess ? le : cudaGetLastError(), "decode_attn launch");
     if (rc) return rc;
   }
   return kOk;

@@ -19,6 +19,9 @@ __global__ void __launch_bounds__(kStoreThreads)
 store_kvcache_kernel(const char* __restrict__ key, const char* __restrict__ value, long long key_stride_b,
                      long long value_stride_b, char* __restrict__ k_cache, char* __restrict__ v_cache,
                      const int* __restrict__ slot_mapping, long long total_vecs, int row_vecs, long long n_slots) {
+  // Let a dependent launch (the decode kernel that follows in the stream) start its prologue
+  // now; it still waits for this grid to finish before it reads the cache.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const long long row_bytes = static_cast<long long>(row_vecs) * 16;
   const long long step = static_cast<long long>(gridDim.x) * kStoreThreads * kStoreUnroll;
   for (long long base = static_cast<long long>(blockIdx.x) * kStoreThreads * kStoreUnroll + threadIdx.x;
