@@ -88,9 +88,12 @@ int b200_device_status(void) {
     cudaError_t e = cudaGetLastError();
     return b200::check_cuda(e == cudaSuccess ? cudaErrorUnknown : e, "device_status: cudaDeviceSynchronize");
   }
-  if (b200::read_status_decode() || b200::read_status_prefill_mma() || b200::read_status_prefill_tc())
-    return b200::set_error(b200::kErrTimeout, "a bounded device-side wait gave up (decode=%d prefill mma=%d tcgen05=%d)",
-                           b200::read_status_decode(), b200::read_status_prefill_mma(), b200::read_status_prefill_tc());
+  if (b200::read_status_decode() || b200::read_status_prefill_mma() || b200::read_status_prefill_tc() ||
+      b200::read_status_prefill_tc2())
+    return b200::set_error(b200::kErrTimeout,
+                           "a bounded device-side wait gave up (decode=%d prefill mma=%d tcgen05=%d tcgen05 persistent=%d)",
+                           b200::read_status_decode(), b200::read_status_prefill_mma(), b200::read_status_prefill_tc(),
+                           b200::read_status_prefill_tc2());
   return b200::kOk;
 }
 

@@ -29,9 +29,14 @@ bool prefill_tc_supports(const PrefillParams& p);
 int launch_prefill_tc(const PrefillParams& p, const CUtensorMap& map_q, const CUtensorMap& map_k,
                       const CUtensorMap& map_v, cudaStream_t stream);
 
+// tcgen05 variant, persistent with two query tiles per CTA sharing each K/V tile (same maps as above).
+int launch_prefill_tc2(PrefillParams p, const CUtensorMap& map_q, const CUtensorMap& map_k, const CUtensorMap& map_v,
+                       cudaStream_t stream);
+
 // Device-side "a bounded wait gave up" flags, one per translation unit, summed by b200_device_status().
 int read_status_decode();
 int read_status_prefill_mma();
 int read_status_prefill_tc();
+int read_status_prefill_tc2();
 
 }  // namespace b200

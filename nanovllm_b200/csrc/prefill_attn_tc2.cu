@@ -1,0 +1,447 @@
+// Varlen causal prefill attention, tcgen05 / TMEM, persistent and ping-ponged: the fast path.
+// Replaces flash_attn_varlen_func as called at nanovllm/layers/attention.py:64-70, for dense K/V
+// and for K/V read from the paged cache.
+//
+// One persistent CTA per SM.  A work item is (sequence, kv head, block of 2 * QT query tokens),
+// QT = 128 / G, handed out through an atomic ticket counter, heaviest query blocks first.  The two
+// halves of the block ("A" = first QT tokens, "B" = next QT) are two independent 128-row tiles that
+// share every K/V tile, so K/V traffic per query row is halved and, more to the point, the tensor
+// core always has the other half's MMA to run while one half is in its softmax:
+//   warp 0        TMA producer: draws tickets, publishes item descriptors, loads Q_A / Q_B and
+//                 feeds two-deep rings of 128-token K tiles and V tiles;
+//   warp 1        one elected thread issues tcgen05.mma:  S_X = Q_X K^T  (M128 N128 K16 x 8) and
+//                 O_X += P_X V  (A operand = P read from TMEM, B = V as MN-major shared memory);
+//   warps 2-5     softmax warpgroup of half A: thread r owns TMEM lane r = one query row; reads S
+//                 with tcgen05.ld, keeps max / sum in registers, writes P (bf16) over S with
+//                 tcgen05.st, rescales O in TMEM only when the row max grew by more than 2^8;
+//   warps 6-9     the same for half B.
+// TMEM: S_A [0,128)  S_B [128,256)  O_A [256,384)  O_B [384,512).  Every mbarrier wait is bounded.
+#include <atomic>
+
+#include "../../include/b200_attn.h"
+#include "kernels.cuh"
+#include "tcgen05.cuh"
+
+namespace b200 {
+extern std::atomic<long long> g_launches;
+
+constexpr int kT2Kv = 128;
+constexpr int kT2Sub = 128 * 128;            // one 64-column sub-tile of a 128-row tile (bytes)
+constexpr int kT2Tile = 2 * kT2Sub;          // 128 rows x 128 dims bf16 = 32 KiB
+constexpr int kT2Threads = 320;
+constexpr int kT2Ring = 2;                   // K ring depth and V ring depth
+constexpr int kT2Items = 4;                  // item descriptors in flight
+constexpr int kT2MaxSeqSmem = 1024;          // sequences whose slot table fits in shared memory
+constexpr float kT2Rescale = 8.0f;
+
+static __device__ int g_status_prefill_tc2 = 0;
+static __device__ unsigned int g_prefill_ticket = 0;
+
+struct T2Item {
+  int seq;        // -1: no more work
+  int h;
+  int q_row;      // global row of the block's first query token
+  int tq0;        // that token's index within the sequence
+  int Lq, Lk;
+  int k_begin;    // dense K/V: first row of the sequence
+  int n[2];       // K/V tiles each half needs (n[1] == 0: half B is empty)
+};
+
+__global__ void __launch_bounds__(kT2Threads, 1)
+prefill_attn_tc2_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap map_q,
+                        const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  unsigned char* sQ = smem;                              // [2][32 KiB]
+  unsigned char* sK = smem + 2 * kT2Tile;                // [kT2Ring][32 KiB]
+  unsigned char* sV = sK + kT2Ring * kT2Tile;            // [kT2Ring][32 KiB]
+  int* s_slot = reinterpret_cast<int*>(sV + kT2Ring * kT2Tile);   // [batch + 1] first slot of every sequence
+  __shared__ __align__(8) uint64_t bar_item_full[kT2Items], bar_item_empty[kT2Items];
+  __shared__ __align__(8) uint64_t bar_q_full[2], bar_q_empty[2];
+  __shared__ __align__(8) uint64_t bar_k_full[kT2Ring], bar_k_empty[kT2Ring], bar_v_full[kT2Ring], bar_v_empty[kT2Ring];
+  __shared__ __align__(8) uint64_t bar_s_full[2], bar_p_full[2], bar_o_final[2], bar_o_free[2];
+  __shared__ __align__(16) T2Item s_item[kT2Items];
+  __shared__ uint32_t s_tmem_base;
+  __shared__ int s_abort;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int G = p.G, QT = p.QT, QB = 2 * p.QT;
+  const bool slot_in_smem = p.batch <= kT2MaxSeqSmem;
+
+  if (tid == 0) {
+    s_abort = 0;
+    for (int i = 0; i < kT2Items; ++i) { mbar_init(&bar_item_full[i], 1); mbar_init(&bar_item_empty[i], 9); }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&bar_q_full[i], 1);
+      mbar_init(&bar_q_empty[i], 1);
+      mbar_init(&bar_s_full[i], 1);
+      mbar_init(&bar_p_full[i], 128);
+      mbar_init(&bar_o_final[i], 1);
+      mbar_init(&bar_o_free[i], 128);
+    }
+    for (int i = 0; i < kT2Ring; ++i) {
+      mbar_init(&bar_k_full[i], 1);
+      mbar_init(&bar_k_empty[i], 1);
+      mbar_init(&bar_v_full[i], 1);
+      mbar_init(&bar_v_empty[i], 1);
+    }
+    mbar_fence_init();
+  }
+  if (slot_in_smem)
+    for (int i = tid; i <= p.batch; i += kT2Threads) s_slot[i] = __ldg(p.cu_q + i) / QB + i;
+  if (warp == 1) {
+    tc::tmem_alloc(&s_tmem_base, 512);
+    tc::tmem_relinquish();
+  }
+  tc::fence_before_sync();
+  __syncthreads();
+  tc::fence_after_sync();
+  const uint32_t tmem = s_tmem_base;
+  volatile int* abort_flag = &s_abort;
+
+  if (warp == 0) {
+    // ================================ TMA producer ================================
+    if (lane == 0) {
+      tma_prefetch_desc(&map_q);
+      tma_prefetch_desc(&map_k);
+      tma_prefetch_desc(&map_v);
+      const unsigned int n_items = static_cast<unsigned int>(p.n_slots) * p.Hkv;
+      int n_pub = 0;            // items published
+      int kt = 0, vt = 0;       // K / V tiles issued so far (ring positions)
+      bool ok = true;
+      while (ok) {
+        // a ticket; each CTA draws until it fails, the last ticket of the launch resets the counter
+        const unsigned int tk = atomicAdd(&g_prefill_ticket, 1u);
+        if (tk == n_items + gridDim.x - 1) atomicExch(&g_prefill_ticket, 0u);
+        T2Item it;
+        it.seq = -1;
+        if (tk < n_items) {
+          const int h = tk % p.Hkv;
+          const int x = p.n_slots - 1 - static_cast<int>(tk / p.Hkv);   // later (heavier) blocks first
+          int lo = 0, hi = p.batch;
+          while (hi - lo > 1) {
+            const int mid = (lo + hi) >> 1;
+            const int f = slot_in_smem ? s_slot[mid] : __ldg(p.cu_q + mid) / QB + mid;
+            if (f <= x) lo = mid; else hi = mid;
+          }
+          const int q_begin = __ldg(p.cu_q + lo), q_end = __ldg(p.cu_q + lo + 1);
+          const int Lq = q_end - q_begin;
+          const int qb = x - (q_begin / QB + lo);
+          if (qb < 0 || qb * QB >= Lq) continue;                        // slot owns no query block
+          const int k_begin = __ldg(p.cu_k + lo);
+          const int Lk = __ldg(p.cu_k + lo + 1) - k_begin;
+          const int shift = Lk - Lq;
+          const int tq0 = qb * QB;
+          const int endA = min(tq0 + QT, Lq), endB = min(tq0 + QB, Lq);
+          it.seq = lo;
+          it.h = h;
+          it.q_row = q_begin + tq0;
+          it.tq0 = tq0;
+          it.Lq = Lq;
+          it.Lk = Lk;
+          it.k_begin = k_begin;
+          it.n[0] = max(0, (min(Lk, shift + endA) + kT2Kv - 1) / kT2Kv);
+          it.n[1] = tq0 + QT < Lq ? max(0, (min(Lk, shift + endB) + kT2Kv - 1) / kT2Kv) : 0;
+        }
+        // publish (an item, or the end marker)
+        const int is = n_pub % kT2Items;
+        if (!mbar_wait(&bar_item_empty[is], ((n_pub / kT2Items) & 1) ^ 1, abort_flag)) { ok = false; break; }
+        s_item[is] = it;
+        mbar_arrive(&bar_item_full[is]);
+        if (it.seq < 0) break;
+        // Q tiles (the buffers are free once every S MMA of the previous item has completed)
+        const uint32_t qph = (n_pub & 1) ^ 1;
+        for (int hx = 0; hx < 2; ++hx) {
+          if (!mbar_wait(&bar_q_empty[hx], qph, abort_flag)) { ok = false; break; }
+          if (hx == 1 && it.n[1] == 0 && it.tq0 + QT >= it.Lq) { mbar_arrive(&bar_q_full[1]); continue; }
+          mbar_expect_tx(&bar_q_full[hx], kT2Tile);
+          tma_load_3d(sQ + hx * kT2Tile, &map_q, &bar_q_full[hx], 0, it.h * G, it.q_row + hx * QT);
+          tma_load_3d(sQ + hx * kT2Tile + kT2Sub, &map_q, &bar_q_full[hx], 64, it.h * G, it.q_row + hx * QT);
+        }
+        if (!ok) break;
+        ++n_pub;
+        // K and V tiles
+        const int n = max(it.n[0], it.n[1]);
+        const int* bt_row = p.block_tables ? p.block_tables + it.seq * p.bt_row_stride : nullptr;
+        for (int j = 0; j < n; ++j) {
+          int row0;
+          if (bt_row) {
+            const int tok0 = j * kT2Kv;
+            const int col = tok0 / p.block_size;
+            const long long blk = col < p.bt_cols ? bt_row[col] : -1;
+            row0 = (blk >= 0 && blk < p.num_blocks) ? static_cast<int>(blk * p.block_size + (tok0 - col * p.block_size))
+                                                    : -kT2Kv;
+          } else {
+            row0 = it.k_begin + j * kT2Kv;
+          }
+          const int ks = kt % kT2Ring;
+          if (!mbar_wait(&bar_k_empty[ks], ((kt / kT2Ring) & 1) ^ 1, abort_flag)) { ok = false; break; }
+          mbar_expect_tx(&bar_k_full[ks], kT2Tile);
+          tma_load_3d(sK + ks * kT2Tile, &map_k, &bar_k_full[ks], 0, it.h, row0);
+          tma_load_3d(sK + ks * kT2Tile + kT2Sub, &map_k, &bar_k_full[ks], 64, it.h, row0);
+          ++kt;
+          const int vs = vt % kT2Ring;
+          if (!mbar_wait(&bar_v_empty[vs], ((vt / kT2Ring) & 1) ^ 1, abort_flag)) { ok = false; break; }
+          mbar_expect_tx(&bar_v_full[vs], kT2Tile);
+          tma_load_3d(sV + vs * kT2Tile, &map_v, &bar_v_full[vs], 0, it.h, row0);
+          tma_load_3d(sV + vs * kT2Tile + kT2Sub, &map_v, &bar_v_full[vs], 64, it.h, row0);
+          ++vt;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ================================ MMA issuer ================================
+    if (lane == 0) {
+      constexpr uint32_t idesc_qk = tc::idesc_bf16_f32(128, 128, false, false);
+      constexpr uint32_t idesc_pv = tc::idesc_bf16_f32(128, 128, false, true);
+      const uint32_t q_addr = smem_u32(sQ), k_addr = smem_u32(sK), v_addr = smem_u32(sV);
+      int n_item = 0, kt = 0, vt = 0;
+      int np[2] = {0, 0};     // P tiles consumed per half (phase of bar_p_full)
+      int no[2] = {0, 0};     // items whose O was read out per half (phase of bar_o_free)
+      bool ok = true;
+      auto issue_s = [&](int hx, int kslot) {
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          const uint32_t off = (ks >> 2) * kT2Sub + (ks & 3) * 32;
+          tc::mma_ss(tmem + hx * 128, tc::smem_desc_sw128(q_addr + hx * kT2Tile + off, 16, 1024),
+                     tc::smem_desc_sw128(k_addr + kslot * kT2Tile + off, 16, 1024), idesc_qk, ks > 0);
+        }
+        tc::commit(&bar_s_full[hx]);
+      };
+      auto issue_pv = [&](int hx, int vslot, bool accumulate) {
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)
+          tc::mma_ts(tmem + 256 + hx * 128, tmem + hx * 128 + ks * 8,
+                     tc::smem_desc_sw128(v_addr + vslot * kT2Tile + ks * 2048, kT2Sub, 1024), idesc_pv, accumulate || ks > 0);
+      };
+      while (ok) {
+        const int is = n_item % kT2Items;
+        if (!mbar_wait(&bar_item_full[is], (n_item / kT2Items) & 1, abort_flag)) break;
+        const T2Item it = s_item[is];
+        mbar_arrive(&bar_item_empty[is]);
+        if (it.seq < 0) break;
+        const int nA = it.n[0], nB = it.n[1], n = max(nA, nB);
+        const uint32_t qph = n_item & 1;
+        if (!mbar_wait(&bar_q_full[0], qph, abort_flag) || !mbar_wait(&bar_q_full[1], qph, abort_flag)) break;
+        // first K tile: S for both halves
+        if (n > 0) {
+          if (!mbar_wait(&bar_k_full[kt % kT2Ring], (kt / kT2Ring) & 1, abort_flag)) break;
+          tc::fence_after_sync();
+          if (nA > 0) issue_s(0, kt % kT2Ring);
+          if (nB > 0) issue_s(1, kt % kT2Ring);
+          tc::commit(&bar_k_empty[kt % kT2Ring]);
+          ++kt;
+        }
+        if (nA <= 1) tc::commit(&bar_q_empty[0]);
+        if (nB <= 1) tc::commit(&bar_q_empty[1]);
+        for (int j = 0; j < n && ok; ++j) {
+          const int vslot = vt % kT2Ring;
+          const uint32_t vph = (vt / kT2Ring) & 1;
+          bool k_next_waited = false;
+          for (int hx = 0; hx < 2 && ok; ++hx) {
+            const int nx = hx == 0 ? nA : nB;
+            if (j >= nx) continue;
+            // O_X += P_X V_j
+            if (!mbar_wait(&bar_p_full[hx], np[hx] & 1, abort_flag)) { ok = false; break; }
+            ++np[hx];
+            if (j == 0 && !mbar_wait(&bar_o_free[hx], (no[hx] & 1) ^ 1, abort_flag)) { ok = false; break; }
+            if (!mbar_wait(&bar_v_full[vslot], vph, abort_flag)) { ok = false; break; }
+            tc::fence_after_sync();
+            issue_pv(hx, vslot, j > 0);
+            if (j == nx - 1) { tc::commit(&bar_o_final[hx]); ++no[hx]; }
+            // S_X for the next K tile (its buffer is free: the PV above reads P before it runs)
+            if (j + 1 < nx) {
+              if (!k_next_waited) {
+                if (!mbar_wait(&bar_k_full[kt % kT2Ring], (kt / kT2Ring) & 1, abort_flag)) { ok = false; break; }
+                tc::fence_after_sync();
+                k_next_waited = true;
+              }
+              issue_s(hx, kt % kT2Ring);
+              if (j + 2 >= nx) tc::commit(&bar_q_empty[hx]);   // that was the half's last S: its Q tile is free
+            }
+          }
+          if (!ok) break;
+          tc::commit(&bar_v_empty[vslot]);
+          ++vt;
+          if (j + 1 < n) { tc::commit(&bar_k_empty[kt % kT2Ring]); ++kt; }
+        }
+        ++n_item;
+      }
+    }
+  } else {
+    // ================================ softmax / epilogue ================================
+    const int hx = (warp - 2) >> 2;                     // which half this warpgroup serves
+    const int quarter = warp & 3;                       // TMEM lanes this warp may touch
+    const int r = quarter * 32 + lane;                  // row of the (token, head) product
+    const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
+    const uint32_t tmem_s = tmem + hx * 128, tmem_o = tmem + 256 + hx * 128;
+    const float c = p.scale_log2;
+    int n_item = 0, ns = 0, n_final = 0, vt_base = 0;
+    bool ok = true;
+    while (ok) {
+      const int is = n_item % kT2Items;
+      if (!mbar_wait(&bar_item_full[is], (n_item / kT2Items) & 1, abort_flag)) break;
+      const T2Item it = s_item[is];
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bar_item_empty[is]);   // this warp has its copy
+      if (it.seq < 0) break;
+      ++n_item;
+      const int nx = it.n[hx];
+      const int n_all = max(it.n[0], it.n[1]);
+      const int shift = it.Lk - it.Lq;
+      const int tok = it.tq0 + hx * QT + r / G;
+      const bool row_ok = r < QT * G && tok < it.Lq;
+      const int kmax = row_ok ? shift + tok : -1;          // last visible key (inclusive)
+      const int first_row_kmax = shift + it.tq0 + hx * QT;
+      float m_used = -INFINITY, l = 0.f;
+      for (int j = 0; j < nx; ++j) {
+        if (!mbar_wait(&bar_s_full[hx], ns & 1, abort_flag)) { ok = false; break; }
+        ++ns;
+        tc::fence_after_sync();
+        const int key0 = j * kT2Kv;
+        const bool need_mask = key0 + kT2Kv - 1 > first_row_kmax;
+        float mx = -INFINITY;
+#pragma unroll
+        for (int cch = 0; cch < 4; ++cch) {
+          uint32_t v[32];
+          tc::ld_32x32b_x32(tmem_s + lane_base + cch * 32, v);
+          tc::wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            float s = __uint_as_float(v[i]);
+            if (need_mask && key0 + cch * 32 + i > kmax) s = -INFINITY;
+            mx = fmaxf(mx, s);
+          }
+        }
+        const float m_new = fmaxf(m_used, mx);
+        if (j == 0) {
+          m_used = m_new;
+        } else {
+          const bool grow = (m_new - m_used) * c > kT2Rescale;
+          if (__any_sync(0xffffffffu, grow)) {
+            const float alpha = grow ? fast_exp2((m_used - m_new) * c) : 1.f;
+            if (grow) { m_used = m_new; l *= alpha; }
+#pragma unroll
+            for (int cch = 0; cch < 4; ++cch) {
+              uint32_t v[32];
+              tc::ld_32x32b_x32(tmem_o + lane_base + cch * 32, v);
+              tc::wait_ld();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+              tc::st_32x32b_x32(tmem_o + lane_base + cch * 32, v);
+            }
+          }
+        }
+        const float mc = (m_used == -INFINITY ? 0.f : m_used) * c;
+#pragma unroll
+        for (int cch = 0; cch < 4; ++cch) {
+          uint32_t v[32];
+          tc::ld_32x32b_x32(tmem_s + lane_base + cch * 32, v);
+          tc::wait_ld();
+          uint32_t pk[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            float p0 = fast_exp2(fmaf(__uint_as_float(v[2 * i]), c, -mc));
+            float p1 = fast_exp2(fmaf(__uint_as_float(v[2 * i + 1]), c, -mc));
+            if (need_mask) {
+              if (key0 + cch * 32 + 2 * i > kmax) p0 = 0.f;
+              if (key0 + cch * 32 + 2 * i + 1 > kmax) p1 = 0.f;
+            }
+            l += p0 + p1;
+            pk[i] = pack_bf16(p0, p1);
+          }
+          tc::st_32x32b_x16(tmem_s + lane_base + cch * 16, pk);
+        }
+        tc::wait_st();
+        if (key0 + kT2Kv > it.Lk) {
+          // ragged last tile of the sequence: V rows past its end are foreign data; zero them so
+          // that 0 * garbage cannot turn into NaN inside the tensor core
+          const int vt = vt_base + j;
+          if (!mbar_wait(&bar_v_full[vt % kT2Ring], (vt / kT2Ring) & 1, abort_flag)) { ok = false; break; }
+          if (key0 + r >= it.Lk) {
+            unsigned char* vrow = sV + (vt % kT2Ring) * kT2Tile + r * 128;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              *reinterpret_cast<uint4*>(vrow + i * 16) = make_uint4(0, 0, 0, 0);
+              *reinterpret_cast<uint4*>(vrow + kT2Sub + i * 16) = make_uint4(0, 0, 0, 0);
+            }
+          }
+          fence_proxy_async_smem();
+        }
+        tc::fence_before_sync();
+        mbar_arrive(&bar_p_full[hx]);
+      }
+      if (!ok) break;
+      vt_base += n_all;
+      if (nx > 0) {
+        if (!mbar_wait(&bar_o_final[hx], n_final & 1, abort_flag)) break;
+        ++n_final;
+        tc::fence_after_sync();
+        const float inv = l > 0.f ? 1.f / l : 0.f;
+        uint4* dst = reinterpret_cast<uint4*>(p.out + (static_cast<long long>(it.q_row + hx * QT + r / G) * p.H + it.h * G + r % G) * 128);
+#pragma unroll
+        for (int cch = 0; cch < 4; ++cch) {
+          uint32_t v[32];
+          tc::ld_32x32b_x32(tmem_o + lane_base + cch * 32, v);
+          tc::wait_ld();
+          if (row_ok) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              uint4 w;
+              w.x = pack_bf16(__uint_as_float(v[8 * i]) * inv, __uint_as_float(v[8 * i + 1]) * inv);
+              w.y = pack_bf16(__uint_as_float(v[8 * i + 2]) * inv, __uint_as_float(v[8 * i + 3]) * inv);
+              w.z = pack_bf16(__uint_as_float(v[8 * i + 4]) * inv, __uint_as_float(v[8 * i + 5]) * inv);
+              w.w = pack_bf16(__uint_as_float(v[8 * i + 6]) * inv, __uint_as_float(v[8 * i + 7]) * inv);
+              dst[cch * 4 + i] = w;
+            }
+          }
+        }
+        tc::fence_before_sync();
+        mbar_arrive(&bar_o_free[hx]);
+      } else if (row_ok) {
+        // no visible key at all (Lk < Lq rows): zeros, as the reference's attention library does
+        uint4* dst = reinterpret_cast<uint4*>(p.out + (static_cast<long long>(it.q_row + hx * QT + r / G) * p.H + it.h * G + r % G) * 128);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) dst[i] = make_uint4(0, 0, 0, 0);
+      }
+    }
+  }
+
+  // ---- teardown: everyone meets, then the allocating warp frees TMEM ----
+  tc::fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc::fence_after_sync();
+    tc::tmem_dealloc(tmem, 512);
+  }
+  if (tid == 0 && s_abort) atomicExch(&g_status_prefill_tc2, 1);
+}
+
+int read_status_prefill_tc2() {
+  int v = 0;
+  cudaMemcpyFromSymbol(&v, g_status_prefill_tc2, sizeof(int));
+  return v;
+}
+
+// Needs whole query heads groups in a 128-row tile.  The query-block slots are laid out for 2 * QT tokens.
+int launch_prefill_tc2(PrefillParams p, const CUtensorMap& map_q, const CUtensorMap& map_k, const CUtensorMap& map_v,
+                       cudaStream_t stream) {
+  p.n_slots = p.total_q / (2 * p.QT) + p.batch;
+  const size_t smem = 1024 + static_cast<size_t>(2 + 2 * kT2Ring) * kT2Tile +
+                      (p.batch <= kT2MaxSeqSmem ? (p.batch + 1) * 4 : 4) + 64;
+  static std::atomic<size_t> configured{0};
+  if (configured.load() < smem) {
+    int rc = check_cuda(cudaFuncSetAttribute(prefill_attn_tc2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
+                        "prefill_attn(tc2): cudaFuncSetAttribute");
+    if (rc) return rc;
+    configured.store(smem);
+  }
+  const int grid = sm_count();
+  if (grid <= 0) return set_error(kErrNoDriver, "prefill_attn: no CUDA device");
+  if (static_cast<long long>(p.n_slots) * p.Hkv > 0x7fffffffLL) return set_error(kErrBadShape, "prefill_attn: too many query blocks");
+  prefill_attn_tc2_kernel<<<grid, kT2Threads, smem, stream>>>(p, map_q, map_k, map_v);
+  g_launches.fetch_add(1);
+  return check_cuda(cudaGetLastError(), "prefill_attn(tc2) launch");
+}
+
+}  // namespace b200
