@@ -11,10 +11,11 @@
 //                 feeds two-deep rings of 128-token K tiles and V tiles;
 //   warp 1        one elected thread issues tcgen05.mma:  S_X = Q_X K^T  (M128 N128 K16 x 8) and
 //                 O_X += P_X V  (A operand = P read from TMEM, B = V as MN-major shared memory);
-//   warps 2-5     softmax warpgroup of half A: thread r owns TMEM lane r = one query row; reads S
+//   warps 4-7     softmax warpgroup of half A: thread r owns TMEM lane r = one query row; reads S
 //                 with tcgen05.ld, keeps max / sum in registers, writes P (bf16) over S with
 //                 tcgen05.st, rescales O in TMEM only when the row max grew by more than 2^8;
-//   warps 6-9     the same for half B.
+//   warps 8-11    the same for half B.  (Warps 2-3 idle; setmaxnreg moves their registers and
+//                 most of the producer's and issuer's to the softmax warpgroups.)
 // TMEM: S_A [0,128)  S_B [128,256)  O_A [256,384)  O_B [384,512).  Every mbarrier wait is bounded.
 #include <atomic>
 
@@ -28,7 +29,7 @@ extern std::atomic<long long> g_launches;
 constexpr int kT2Kv = 128;
 constexpr int kT2Sub = 128 * 128;            // one 64-column sub-tile of a 128-row tile (bytes)
 constexpr int kT2Tile = 2 * kT2Sub;          // 128 rows x 128 dims bf16 = 32 KiB
-constexpr int kT2Threads = 320;
+constexpr int kT2Threads = 384;   // warpgroup 0: TMA producer, MMA issuer, two idle warps; warpgroups 1, 2: softmax
 constexpr int kT2Ring = 2;                   // K ring depth and V ring depth
 constexpr int kT2Items = 4;                  // item descriptors in flight
 constexpr int kT2MaxSeqSmem = 1024;          // sequences whose slot table fits in shared memory
@@ -99,6 +100,10 @@ prefill_attn_tc2_kernel(const PrefillParams p, const __grid_constant__ CUtensorM
   const uint32_t tmem = s_tmem_base;
   volatile int* abort_flag = &s_abort;
 
+  // Registers move from the light warpgroup to the two softmax warpgroups, which hold a whole
+  // 128-column S row (and later the O row) per thread.
+  if (warp < 4) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 88;" ::: "memory");
   if (warp == 0) {
     // ================================ TMA producer ================================
     if (lane == 0) {
@@ -268,9 +273,11 @@ prefill_attn_tc2_kernel(const PrefillParams p, const __grid_constant__ CUtensorM
         ++n_item;
       }
     }
+  }
   } else {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 208;" ::: "memory");
     // ================================ softmax / epilogue ================================
-    const int hx = (warp - 2) >> 2;                     // which half this warpgroup serves
+    const int hx = (warp - 4) >> 2;                     // which half this warpgroup serves
     const int quarter = warp & 3;                       // TMEM lanes this warp may touch
     const int r = quarter * 32 + lane;                  // row of the (token, head) product
     const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
@@ -300,19 +307,23 @@ prefill_attn_tc2_kernel(const PrefillParams p, const __grid_constant__ CUtensorM
         tc::fence_after_sync();
         const int key0 = j * kT2Kv;
         const bool need_mask = key0 + kT2Kv - 1 > first_row_kmax;
+        // the whole S row in registers: four TMEM loads in flight, one wait
+        uint32_t sv[4][32];
+#pragma unroll
+        for (int cch = 0; cch < 4; ++cch) tc::ld_32x32b_x32(tmem_s + lane_base + cch * 32, sv[cch]);
+        tc::wait_ld();
+        if (need_mask) {
+#pragma unroll
+          for (int cch = 0; cch < 4; ++cch)
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (key0 + cch * 32 + i > kmax) sv[cch][i] = 0xff800000u;   // -inf
+        }
         float mx = -INFINITY;
 #pragma unroll
-        for (int cch = 0; cch < 4; ++cch) {
-          uint32_t v[32];
-          tc::ld_32x32b_x32(tmem_s + lane_base + cch * 32, v);
-          tc::wait_ld();
+        for (int cch = 0; cch < 4; ++cch)
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            float s = __uint_as_float(v[i]);
-            if (need_mask && key0 + cch * 32 + i > kmax) s = -INFINITY;
-            mx = fmaxf(mx, s);
-          }
-        }
+          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(sv[cch][i]));
         const float m_new = fmaxf(m_used, mx);
         if (j == 0) {
           m_used = m_new;
@@ -332,21 +343,15 @@ prefill_attn_tc2_kernel(const PrefillParams p, const __grid_constant__ CUtensorM
             }
           }
         }
+        // P = exp2(c * (s - m)) (masked entries are -inf -> 0), row sum, packed bf16 back over S
         const float mc = (m_used == -INFINITY ? 0.f : m_used) * c;
 #pragma unroll
         for (int cch = 0; cch < 4; ++cch) {
-          uint32_t v[32];
-          tc::ld_32x32b_x32(tmem_s + lane_base + cch * 32, v);
-          tc::wait_ld();
           uint32_t pk[16];
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
-            float p0 = fast_exp2(fmaf(__uint_as_float(v[2 * i]), c, -mc));
-            float p1 = fast_exp2(fmaf(__uint_as_float(v[2 * i + 1]), c, -mc));
-            if (need_mask) {
-              if (key0 + cch * 32 + 2 * i > kmax) p0 = 0.f;
-              if (key0 + cch * 32 + 2 * i + 1 > kmax) p1 = 0.f;
-            }
+            const float p0 = fast_exp2(fmaf(__uint_as_float(sv[cch][2 * i]), c, -mc));
+            const float p1 = fast_exp2(fmaf(__uint_as_float(sv[cch][2 * i + 1]), c, -mc));
             l += p0 + p1;
             pk[i] = pack_bf16(p0, p1);
           }
@@ -379,25 +384,27 @@ prefill_attn_tc2_kernel(const PrefillParams p, const __grid_constant__ CUtensorM
         tc::fence_after_sync();
         const float inv = l > 0.f ? 1.f / l : 0.f;
         uint4* dst = reinterpret_cast<uint4*>(p.out + (static_cast<long long>(it.q_row + hx * QT + r / G) * p.H + it.h * G + r % G) * 128);
+        uint32_t ov[4][32];
 #pragma unroll
-        for (int cch = 0; cch < 4; ++cch) {
-          uint32_t v[32];
-          tc::ld_32x32b_x32(tmem_o + lane_base + cch * 32, v);
-          tc::wait_ld();
-          if (row_ok) {
+        for (int cch = 0; cch < 4; ++cch) tc::ld_32x32b_x32(tmem_o + lane_base + cch * 32, ov[cch]);
+        tc::wait_ld();
+        // O is in registers: the accumulator may be overwritten by the next item already
+        tc::fence_before_sync();
+        mbar_arrive(&bar_o_free[hx]);
+        if (row_ok) {
+#pragma unroll
+          for (int cch = 0; cch < 4; ++cch) {
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
               uint4 w;
-              w.x = pack_bf16(__uint_as_float(v[8 * i]) * inv, __uint_as_float(v[8 * i + 1]) * inv);
-              w.y = pack_bf16(__uint_as_float(v[8 * i + 2]) * inv, __uint_as_float(v[8 * i + 3]) * inv);
-              w.z = pack_bf16(__uint_as_float(v[8 * i + 4]) * inv, __uint_as_float(v[8 * i + 5]) * inv);
-              w.w = pack_bf16(__uint_as_float(v[8 * i + 6]) * inv, __uint_as_float(v[8 * i + 7]) * inv);
+              w.x = pack_bf16(__uint_as_float(ov[cch][8 * i]) * inv, __uint_as_float(ov[cch][8 * i + 1]) * inv);
+              w.y = pack_bf16(__uint_as_float(ov[cch][8 * i + 2]) * inv, __uint_as_float(ov[cch][8 * i + 3]) * inv);
+              w.z = pack_bf16(__uint_as_float(ov[cch][8 * i + 4]) * inv, __uint_as_float(ov[cch][8 * i + 5]) * inv);
+              w.w = pack_bf16(__uint_as_float(ov[cch][8 * i + 6]) * inv, __uint_as_float(ov[cch][8 * i + 7]) * inv);
               dst[cch * 4 + i] = w;
             }
           }
         }
-        tc::fence_before_sync();
-        mbar_arrive(&bar_o_free[hx]);
       } else if (row_ok) {
         // no visible key at all (Lk < Lq rows): zeros, as the reference's attention library does
         uint4* dst = reinterpret_cast<uint4*>(p.out + (static_cast<long long>(it.q_row + hx * QT + r / G) * p.H + it.h * G + r % G) * 128);
