@@ -272,7 +272,7 @@ def run_decode(args, w, rank, world, local):
 
 
 # dram bytes per launch of the dominant kernel from the committed ncu captures (profiles/), or None
-TRAFFIC = {}
+TRAFFIC = {"decode_cfg2": 1145381544}   # dram read + write per launch, profiles/decode_attn_kernel_decode_cfg2.md
 
 
 # --------------------------------------------------------------------------------------------
