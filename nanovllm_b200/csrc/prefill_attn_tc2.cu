@@ -36,6 +36,22 @@ constexpr int kT2MaxSeqSmem = 1024;          // sequences whose slot table fits 
 constexpr float kT2Rescale = 8.0f;
 
 static __device__ int g_status_prefill_tc2 = 0;
+
+// Optional per-item timestamps of CTA 0..7 (compile with -DB200_TRACE; read with b200_debug_trace_prefill).
+#ifdef B200_TRACE
+constexpr int kT2TraceItems = 96, kT2TraceSlots = 12;
+__device__ unsigned long long g_pf_trace[8 * kT2TraceItems * kT2TraceSlots];
+__device__ __forceinline__ void pf_trace(int item, int slot, unsigned long long extra = 0) {
+  if (blockIdx.x < 8 && item < kT2TraceItems) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    g_pf_trace[(blockIdx.x * kT2TraceItems + item) * kT2TraceSlots + slot] = extra ? extra : t;
+  }
+}
+#define PF_TRACE(...) pf_trace(__VA_ARGS__)
+#else
+#define PF_TRACE(...) do { } while (0)
+#endif
 static __device__ unsigned int g_prefill_ticket = 0;
 
 struct T2Item {
@@ -76,9 +92,9 @@ prefill_attn_tc2_kernel(const PrefillParams p, const __grid_constant__ CUtensorM
       mbar_init(&bar_q_full[i], 1);
       mbar_init(&bar_q_empty[i], 1);
       mbar_init(&bar_s_full[i], 1);
-      mbar_init(&bar_p_full[i], 128);
+      mbar_init(&bar_p_full[i], 4);
       mbar_init(&bar_o_final[i], 1);
-      mbar_init(&bar_o_free[i], 128);
+      mbar_init(&bar_o_free[i], 4);
     }
     for (int i = 0; i < kT2Ring; ++i) {
       mbar_init(&bar_k_full[i], 1);
@@ -154,6 +170,8 @@ prefill_attn_tc2_kernel(const PrefillParams p, const __grid_constant__ CUtensorM
         s_item[is] = it;
         mbar_arrive(&bar_item_full[is]);
         if (it.seq < 0) break;
+        PF_TRACE(n_pub, 0);
+        PF_TRACE(n_pub, 11, (static_cast<unsigned long long>(it.n[0]) << 8) | it.n[1] | (1ull << 32));
         // Q tiles (the buffers are free once every S MMA of the previous item has completed)
         const uint32_t qph = (n_pub & 1) ^ 1;
         for (int hx = 0; hx < 2; ++hx) {
@@ -164,6 +182,7 @@ prefill_attn_tc2_kernel(const PrefillParams p, const __grid_constant__ CUtensorM
           tma_load_3d(sQ + hx * kT2Tile + kT2Sub, &map_q, &bar_q_full[hx], 64, it.h * G, it.q_row + hx * QT);
         }
         if (!ok) break;
+        PF_TRACE(n_pub, 1);
         ++n_pub;
         // K and V tiles
         const int n = max(it.n[0], it.n[1]);
@@ -225,9 +244,11 @@ prefill_attn_tc2_kernel(const PrefillParams p, const __grid_constant__ CUtensorM
         const T2Item it = s_item[is];
         mbar_arrive(&bar_item_empty[is]);
         if (it.seq < 0) break;
+        PF_TRACE(n_item, 2);
         const int nA = it.n[0], nB = it.n[1], n = max(nA, nB);
         const uint32_t qph = n_item & 1;
         if (!mbar_wait(&bar_q_full[0], qph, abort_flag) || !mbar_wait(&bar_q_full[1], qph, abort_flag)) break;
+        PF_TRACE(n_item, 3);
         // first K tile: S for both halves
         if (n > 0) {
           if (!mbar_wait(&bar_k_full[kt % kT2Ring], (kt / kT2Ring) & 1, abort_flag)) break;
@@ -236,6 +257,7 @@ prefill_attn_tc2_kernel(const PrefillParams p, const __grid_constant__ CUtensorM
           if (nB > 0) issue_s(1, kt % kT2Ring);
           tc::commit(&bar_k_empty[kt % kT2Ring]);
           ++kt;
+          PF_TRACE(n_item, 4);
         }
         if (nA <= 1) tc::commit(&bar_q_empty[0]);
         if (nB <= 1) tc::commit(&bar_q_empty[1]);
@@ -270,6 +292,7 @@ prefill_attn_tc2_kernel(const PrefillParams p, const __grid_constant__ CUtensorM
           ++vt;
           if (j + 1 < n) { tc::commit(&bar_k_empty[kt % kT2Ring]); ++kt; }
         }
+        PF_TRACE(n_item, 5);
         ++n_item;
       }
     }
@@ -285,6 +308,12 @@ prefill_attn_tc2_kernel(const PrefillParams p, const __grid_constant__ CUtensorM
     const float c = p.scale_log2;
     int n_item = 0, ns = 0, n_final = 0, vt_base = 0;
     bool ok = true;
+#ifdef B200_TRACE
+    long long ck_wait = 0, ck_ld = 0, ck_max = 0, ck_exp = 0, ck_sig = 0, ck_epi = 0, ck_tiles = 0, ck_t0 = 0;
+#define CK(var) do { const long long now_ = clock64(); var += now_ - ck_t0; ck_t0 = now_; } while (0)
+#else
+#define CK(var) do { } while (0)
+#endif
     while (ok) {
       const int is = n_item % kT2Items;
       if (!mbar_wait(&bar_item_full[is], (n_item / kT2Items) & 1, abort_flag)) break;
@@ -302,8 +331,13 @@ prefill_attn_tc2_kernel(const PrefillParams p, const __grid_constant__ CUtensorM
       const int first_row_kmax = shift + it.tq0 + hx * QT;
       float m_used = -INFINITY, l = 0.f;
       for (int j = 0; j < nx; ++j) {
+#ifdef B200_TRACE
+        ck_t0 = clock64(); ++ck_tiles;
+#endif
         if (!mbar_wait(&bar_s_full[hx], ns & 1, abort_flag)) { ok = false; break; }
+        CK(ck_wait);
         ++ns;
+        if (hx == 0 && r == 0 && j == 0) PF_TRACE(n_item - 1, 6);
         tc::fence_after_sync();
         const int key0 = j * kT2Kv;
         const bool need_mask = key0 + kT2Kv - 1 > first_row_kmax;
@@ -312,6 +346,7 @@ prefill_attn_tc2_kernel(const PrefillParams p, const __grid_constant__ CUtensorM
 #pragma unroll
         for (int cch = 0; cch < 4; ++cch) tc::ld_32x32b_x32(tmem_s + lane_base + cch * 32, sv[cch]);
         tc::wait_ld();
+        CK(ck_ld);
         if (need_mask) {
 #pragma unroll
           for (int cch = 0; cch < 4; ++cch)
@@ -319,11 +354,24 @@ prefill_attn_tc2_kernel(const PrefillParams p, const __grid_constant__ CUtensorM
             for (int i = 0; i < 32; ++i)
               if (key0 + cch * 32 + i > kmax) sv[cch][i] = 0xff800000u;   // -inf
         }
-        float mx = -INFINITY;
+        // eight independent max chains (a single chain of 128 dependent FMNMX costs ~500 cycles)
+        float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+        float mx4 = -INFINITY, mx5 = -INFINITY, mx6 = -INFINITY, mx7 = -INFINITY;
 #pragma unroll
-        for (int cch = 0; cch < 4; ++cch)
+        for (int cch = 0; cch < 4; ++cch) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(sv[cch][i]));
+          for (int i = 0; i < 32; i += 8) {
+            mx0 = fmaxf(mx0, __uint_as_float(sv[cch][i]));
+            mx1 = fmaxf(mx1, __uint_as_float(sv[cch][i + 1]));
+            mx2 = fmaxf(mx2, __uint_as_float(sv[cch][i + 2]));
+            mx3 = fmaxf(mx3, __uint_as_float(sv[cch][i + 3]));
+            mx4 = fmaxf(mx4, __uint_as_float(sv[cch][i + 4]));
+            mx5 = fmaxf(mx5, __uint_as_float(sv[cch][i + 5]));
+            mx6 = fmaxf(mx6, __uint_as_float(sv[cch][i + 6]));
+            mx7 = fmaxf(mx7, __uint_as_float(sv[cch][i + 7]));
+          }
+        }
+        const float mx = fmaxf(fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)), fmaxf(fmaxf(mx4, mx5), fmaxf(mx6, mx7)));
         const float m_new = fmaxf(m_used, mx);
         if (j == 0) {
           m_used = m_new;
@@ -343,20 +391,36 @@ prefill_attn_tc2_kernel(const PrefillParams p, const __grid_constant__ CUtensorM
             }
           }
         }
+        CK(ck_max);
         // P = exp2(c * (s - m)) (masked entries are -inf -> 0), row sum, packed bf16 back over S
         const float mc = (m_used == -INFINITY ? 0.f : m_used) * c;
+        float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;   // four independent sum chains
 #pragma unroll
         for (int cch = 0; cch < 4; ++cch) {
           uint32_t pk[16];
 #pragma unroll
-          for (int i = 0; i < 16; ++i) {
+          for (int i = 0; i < 16; i += 4) {
             const float p0 = fast_exp2(fmaf(__uint_as_float(sv[cch][2 * i]), c, -mc));
             const float p1 = fast_exp2(fmaf(__uint_as_float(sv[cch][2 * i + 1]), c, -mc));
-            l += p0 + p1;
+            const float p2 = fast_exp2(fmaf(__uint_as_float(sv[cch][2 * i + 2]), c, -mc));
+            const float p3 = fast_exp2(fmaf(__uint_as_float(sv[cch][2 * i + 3]), c, -mc));
+            const float p4 = fast_exp2(fmaf(__uint_as_float(sv[cch][2 * i + 4]), c, -mc));
+            const float p5 = fast_exp2(fmaf(__uint_as_float(sv[cch][2 * i + 5]), c, -mc));
+            const float p6 = fast_exp2(fmaf(__uint_as_float(sv[cch][2 * i + 6]), c, -mc));
+            const float p7 = fast_exp2(fmaf(__uint_as_float(sv[cch][2 * i + 7]), c, -mc));
+            l0 += p0 + p1;
+            l1 += p2 + p3;
+            l2 += p4 + p5;
+            l3 += p6 + p7;
             pk[i] = pack_bf16(p0, p1);
+            pk[i + 1] = pack_bf16(p2, p3);
+            pk[i + 2] = pack_bf16(p4, p5);
+            pk[i + 3] = pack_bf16(p6, p7);
           }
           tc::st_32x32b_x16(tmem_s + lane_base + cch * 16, pk);
         }
+        l += (l0 + l1) + (l2 + l3);
+        CK(ck_exp);
         tc::wait_st();
         if (key0 + kT2Kv > it.Lk) {
           // ragged last tile of the sequence: V rows past its end are foreign data; zero them so
@@ -374,13 +438,20 @@ prefill_attn_tc2_kernel(const PrefillParams p, const __grid_constant__ CUtensorM
           fence_proxy_async_smem();
         }
         tc::fence_before_sync();
-        mbar_arrive(&bar_p_full[hx]);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bar_p_full[hx]);   // one arrival per warp
+        CK(ck_sig);
+        if (hx == 0 && r == 0 && j == nx - 1) PF_TRACE(n_item - 1, 7);
       }
       if (!ok) break;
       vt_base += n_all;
       if (nx > 0) {
+#ifdef B200_TRACE
+        ck_t0 = clock64();
+#endif
         if (!mbar_wait(&bar_o_final[hx], n_final & 1, abort_flag)) break;
         ++n_final;
+        if (hx == 0 && r == 0) PF_TRACE(n_item - 1, 8);
         tc::fence_after_sync();
         const float inv = l > 0.f ? 1.f / l : 0.f;
         uint4* dst = reinterpret_cast<uint4*>(p.out + (static_cast<long long>(it.q_row + hx * QT + r / G) * p.H + it.h * G + r % G) * 128);
@@ -390,7 +461,8 @@ prefill_attn_tc2_kernel(const PrefillParams p, const __grid_constant__ CUtensorM
         tc::wait_ld();
         // O is in registers: the accumulator may be overwritten by the next item already
         tc::fence_before_sync();
-        mbar_arrive(&bar_o_free[hx]);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bar_o_free[hx]);
         if (row_ok) {
 #pragma unroll
           for (int cch = 0; cch < 4; ++cch) {
@@ -405,6 +477,8 @@ prefill_attn_tc2_kernel(const PrefillParams p, const __grid_constant__ CUtensorM
             }
           }
         }
+        CK(ck_epi);
+        if (hx == 0 && r == 0) PF_TRACE(n_item - 1, 9);
       } else if (row_ok) {
         // no visible key at all (Lk < Lq rows): zeros, as the reference's attention library does
         uint4* dst = reinterpret_cast<uint4*>(p.out + (static_cast<long long>(it.q_row + hx * QT + r / G) * p.H + it.h * G + r % G) * 128);
@@ -412,8 +486,19 @@ prefill_attn_tc2_kernel(const PrefillParams p, const __grid_constant__ CUtensorM
         for (int i = 0; i < 16; ++i) dst[i] = make_uint4(0, 0, 0, 0);
       }
     }
+#ifdef B200_TRACE
+    if (hx == 0 && r == 0 && blockIdx.x < 8) {
+      unsigned long long* o = g_pf_trace + (blockIdx.x * kT2TraceItems + (kT2TraceItems - 1)) * kT2TraceSlots;
+      o[0] = ck_tiles; o[1] = ck_wait; o[2] = ck_ld; o[3] = ck_max; o[4] = ck_exp; o[5] = ck_sig; o[6] = ck_epi; o[7] = n_item;
+    }
+#endif
   }
 
+#ifdef B200_TRACE
+  if (warp == 4 && lane == 0 && blockIdx.x < 8) {
+    // reuse the last trace rows of the CTA for the cycle breakdown of softmax warpgroup A, thread 0
+  }
+#endif
   // ---- teardown: everyone meets, then the allocating warp frees TMEM ----
   tc::fence_before_sync();
   __syncthreads();
@@ -423,6 +508,12 @@ prefill_attn_tc2_kernel(const PrefillParams p, const __grid_constant__ CUtensorM
   }
   if (tid == 0 && s_abort) atomicExch(&g_status_prefill_tc2, 1);
 }
+
+#ifdef B200_TRACE
+extern "C" int b200_debug_trace_prefill(unsigned long long* host_out, int n) {
+  return static_cast<int>(cudaMemcpyFromSymbol(host_out, g_pf_trace, sizeof(unsigned long long) * n));
+}
+#endif
 
 int read_status_prefill_tc2() {
   int v = 0;
