@@ -89,7 +89,7 @@ int b200_device_status(void) {
     return b200::check_cuda(e == cudaSuccess ? cudaErrorUnknown : e, "device_status: cudaDeviceSynchronize");
   }
   if (b200::read_status_decode() || b200::read_status_prefill_mma() || b200::read_status_prefill_tc() ||
-      b200::read_status_prefill_tc2())
+      b200::read_status_prefill_tc2() || b200::read_status_prefill_tc3())
     return b200::set_error(b200::kErrTimeout,
                            "a bounded device-side wait gave up (decode=%d prefill mma=%d tcgen05=%d tcgen05 persistent=%d)",
                            b200::read_status_decode(), b200::read_status_prefill_mma(), b200::read_status_prefill_tc(),

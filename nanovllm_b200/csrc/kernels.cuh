@@ -33,10 +33,15 @@ int launch_prefill_tc(const PrefillParams& p, const CUtensorMap& map_q, const CU
 int launch_prefill_tc2(PrefillParams p, const CUtensorMap& map_q, const CUtensorMap& map_k, const CUtensorMap& map_v,
                        cudaStream_t stream);
 
+// tcgen05 variant, persistent, 64-key steps with double-buffered S (K/V maps with 64-token boxes).
+int launch_prefill_tc3(PrefillParams p, const CUtensorMap& map_q, const CUtensorMap& map_k, const CUtensorMap& map_v,
+                       cudaStream_t stream);
+
 // Device-side "a bounded wait gave up" flags, one per translation unit, summed by b200_device_status().
 int read_status_decode();
 int read_status_prefill_mma();
 int read_status_prefill_tc();
 int read_status_prefill_tc2();
+int read_status_prefill_tc3();
 
 }  // namespace b200
