@@ -64,6 +64,57 @@ struct T2Item {
   int n[2];       // K/V tiles each half needs (n[1] == 0: half B is empty)
 };
 
+// Output of one half of an item: read the finished O row out of TMEM, release the accumulator
+// (and, if given, hand the first P of the next item to the issuer), then scale by 1 / row sum and
+// store bf16 rows through a per-warp staging tile so that every store instruction writes 64-byte
+// row segments (a thread owns a whole row: stored directly, each instruction would touch 32
+// different lines with 16 bytes each).
+__device__ __forceinline__ bool t2_epilogue(const PrefillParams& p, uint32_t tmem_o_lane, uint64_t* bar_o_final,
+                                            uint32_t parity, uint64_t* bar_o_free, uint64_t* bar_p_full,
+                                            volatile int* abort_flag, unsigned char* stage, int lane, int quarter, int hx,
+                                            float inv, int q_row, int h, int tq0, int Lq) {
+  if (!mbar_wait(bar_o_final, parity, abort_flag)) return false;
+  tc::fence_after_sync();
+  uint32_t ov[4][32];
+#pragma unroll
+  for (int cch = 0; cch < 4; ++cch) tc::ld_32x32b_x32(tmem_o_lane + cch * 32, ov[cch]);
+  tc::wait_ld();
+  tc::fence_before_sync();
+  __syncwarp();
+  if (lane == 0) {
+    mbar_arrive(bar_o_free);
+    if (bar_p_full) mbar_arrive(bar_p_full);
+  }
+  const int G = p.G, QT = p.QT;
+  const int srow = (lane >> 2), sq = lane & 3;           // read-back role: 8 rows x 4 chunks per instruction
+#pragma unroll
+  for (int cch = 0; cch < 4; ++cch) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      uint4 w;
+      w.x = pack_bf16(__uint_as_float(ov[cch][8 * i]) * inv, __uint_as_float(ov[cch][8 * i + 1]) * inv);
+      w.y = pack_bf16(__uint_as_float(ov[cch][8 * i + 2]) * inv, __uint_as_float(ov[cch][8 * i + 3]) * inv);
+      w.z = pack_bf16(__uint_as_float(ov[cch][8 * i + 4]) * inv, __uint_as_float(ov[cch][8 * i + 5]) * inv);
+      w.w = pack_bf16(__uint_as_float(ov[cch][8 * i + 6]) * inv, __uint_as_float(ov[cch][8 * i + 7]) * inv);
+      *reinterpret_cast<uint4*>(stage + lane * 64 + ((i ^ ((lane >> 1) & 3)) << 4)) = w;
+    }
+    __syncwarp();
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int lr = 8 * k + srow;                          // row within the warp's 32
+      const uint4 w = *reinterpret_cast<const uint4*>(stage + lr * 64 + ((sq ^ ((lr >> 1) & 3)) << 4));
+      const int rr = quarter * 32 + lr;                     // row of the 128-row tile
+      const int tk = tq0 + hx * QT + rr / G;
+      if (rr < QT * G && tk < Lq)
+        *reinterpret_cast<uint4*>(reinterpret_cast<unsigned char*>(
+            p.out + (static_cast<long long>(q_row + hx * QT + rr / G) * p.H + h * G + rr % G) * 128) +
+            cch * 64 + sq * 16) = w;
+    }
+    __syncwarp();
+  }
+  return true;
+}
+
 __global__ void __launch_bounds__(kT2Threads, 1)
 prefill_attn_tc2_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap map_q,
                         const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v) {
@@ -72,7 +123,8 @@ prefill_attn_tc2_kernel(const PrefillParams p, const __grid_constant__ CUtensorM
   unsigned char* sQ = smem;                              // [2][32 KiB]
   unsigned char* sK = smem + 2 * kT2Tile;                // [kT2Ring][32 KiB]
   unsigned char* sV = sK + kT2Ring * kT2Tile;            // [kT2Ring][32 KiB]
-  int* s_slot = reinterpret_cast<int*>(sV + kT2Ring * kT2Tile);   // [batch + 1] first slot of every sequence
+  unsigned char* sStage = sV + kT2Ring * kT2Tile;       // [8 softmax warps][32 rows x 64 B] output staging
+  int* s_slot = reinterpret_cast<int*>(sStage + 8 * 2048);       // [batch + 1] first slot of every sequence
   __shared__ __align__(8) uint64_t bar_item_full[kT2Items], bar_item_empty[kT2Items];
   __shared__ __align__(8) uint64_t bar_q_full[2], bar_q_empty[2];
   __shared__ __align__(8) uint64_t bar_k_full[kT2Ring], bar_k_empty[kT2Ring], bar_v_full[kT2Ring], bar_v_empty[kT2Ring];
@@ -308,6 +360,13 @@ prefill_attn_tc2_kernel(const PrefillParams p, const __grid_constant__ CUtensorM
     const float c = p.scale_log2;
     int n_item = 0, ns = 0, n_final = 0, vt_base = 0;
     bool ok = true;
+    // The output of an item leaves one step late: its O row is read out of TMEM right before the
+    // first P of the NEXT item is handed to the issuer, and converted / stored while the tensor
+    // core runs that item's first PV, instead of stalling this warpgroup at the item boundary.
+    bool pend = false;
+    float pend_inv = 0.f;
+    int pend_q_row = 0, pend_h = 0, pend_tq0 = 0, pend_Lq = 0;
+
 #ifdef B200_TRACE
     long long ck_wait = 0, ck_ld = 0, ck_max = 0, ck_exp = 0, ck_sig = 0, ck_epi = 0, ck_tiles = 0, ck_t0 = 0;
 #define CK(var) do { const long long now_ = clock64(); var += now_ - ck_t0; ck_t0 = now_; } while (0)
@@ -348,30 +407,34 @@ prefill_attn_tc2_kernel(const PrefillParams p, const __grid_constant__ CUtensorM
         tc::wait_ld();
         CK(ck_ld);
         if (need_mask) {
+          const int nvalid = kmax - key0 + 1;           // columns of this row that may be seen
 #pragma unroll
-          for (int cch = 0; cch < 4; ++cch)
+          for (int cch = 0; cch < 4; ++cch) {
+            if (nvalid < (cch + 1) * 32) {              // a chunk that lies wholly below the diagonal costs nothing
 #pragma unroll
-            for (int i = 0; i < 32; ++i)
-              if (key0 + cch * 32 + i > kmax) sv[cch][i] = 0xff800000u;   // -inf
+              for (int i = 0; i < 32; ++i)
+                if (cch * 32 + i >= nvalid) sv[cch][i] = 0xff800000u;   // -inf
+            }
+          }
         }
-        // eight independent max chains (a single chain of 128 dependent FMNMX costs ~500 cycles)
+        // eight independent chains of 3-input max
         float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
         float mx4 = -INFINITY, mx5 = -INFINITY, mx6 = -INFINITY, mx7 = -INFINITY;
 #pragma unroll
         for (int cch = 0; cch < 4; ++cch) {
 #pragma unroll
-          for (int i = 0; i < 32; i += 8) {
-            mx0 = fmaxf(mx0, __uint_as_float(sv[cch][i]));
-            mx1 = fmaxf(mx1, __uint_as_float(sv[cch][i + 1]));
-            mx2 = fmaxf(mx2, __uint_as_float(sv[cch][i + 2]));
-            mx3 = fmaxf(mx3, __uint_as_float(sv[cch][i + 3]));
-            mx4 = fmaxf(mx4, __uint_as_float(sv[cch][i + 4]));
-            mx5 = fmaxf(mx5, __uint_as_float(sv[cch][i + 5]));
-            mx6 = fmaxf(mx6, __uint_as_float(sv[cch][i + 6]));
-            mx7 = fmaxf(mx7, __uint_as_float(sv[cch][i + 7]));
+          for (int i = 0; i < 32; i += 16) {
+            mx0 = fmax3(mx0, __uint_as_float(sv[cch][i]), __uint_as_float(sv[cch][i + 1]));
+            mx1 = fmax3(mx1, __uint_as_float(sv[cch][i + 2]), __uint_as_float(sv[cch][i + 3]));
+            mx2 = fmax3(mx2, __uint_as_float(sv[cch][i + 4]), __uint_as_float(sv[cch][i + 5]));
+            mx3 = fmax3(mx3, __uint_as_float(sv[cch][i + 6]), __uint_as_float(sv[cch][i + 7]));
+            mx4 = fmax3(mx4, __uint_as_float(sv[cch][i + 8]), __uint_as_float(sv[cch][i + 9]));
+            mx5 = fmax3(mx5, __uint_as_float(sv[cch][i + 10]), __uint_as_float(sv[cch][i + 11]));
+            mx6 = fmax3(mx6, __uint_as_float(sv[cch][i + 12]), __uint_as_float(sv[cch][i + 13]));
+            mx7 = fmax3(mx7, __uint_as_float(sv[cch][i + 14]), __uint_as_float(sv[cch][i + 15]));
           }
         }
-        const float mx = fmaxf(fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)), fmaxf(fmaxf(mx4, mx5), fmaxf(mx6, mx7)));
+        const float mx = fmax3(fmax3(mx0, mx1, mx2), fmax3(mx3, mx4, mx5), fmaxf(mx6, mx7));
         const float m_new = fmaxf(m_used, mx);
         if (j == 0) {
           m_used = m_new;
@@ -394,30 +457,37 @@ prefill_attn_tc2_kernel(const PrefillParams p, const __grid_constant__ CUtensorM
         CK(ck_max);
         // P = exp2(c * (s - m)) (masked entries are -inf -> 0), row sum, packed bf16 back over S
         const float mc = (m_used == -INFINITY ? 0.f : m_used) * c;
-        float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;   // four independent sum chains
+        // packed 2 x fp32 FMA and ADD: half the instructions of the scalar form
+        const unsigned long long c2 = f32x2_pack(c, c), nmc2 = f32x2_pack(-mc, -mc);
+        unsigned long long ls0 = 0ull, ls1 = 0ull, ls2 = 0ull, ls3 = 0ull;   // four independent (pair) sum chains
 #pragma unroll
         for (int cch = 0; cch < 4; ++cch) {
           uint32_t pk[16];
 #pragma unroll
           for (int i = 0; i < 16; i += 4) {
-            const float p0 = fast_exp2(fmaf(__uint_as_float(sv[cch][2 * i]), c, -mc));
-            const float p1 = fast_exp2(fmaf(__uint_as_float(sv[cch][2 * i + 1]), c, -mc));
-            const float p2 = fast_exp2(fmaf(__uint_as_float(sv[cch][2 * i + 2]), c, -mc));
-            const float p3 = fast_exp2(fmaf(__uint_as_float(sv[cch][2 * i + 3]), c, -mc));
-            const float p4 = fast_exp2(fmaf(__uint_as_float(sv[cch][2 * i + 4]), c, -mc));
-            const float p5 = fast_exp2(fmaf(__uint_as_float(sv[cch][2 * i + 5]), c, -mc));
-            const float p6 = fast_exp2(fmaf(__uint_as_float(sv[cch][2 * i + 6]), c, -mc));
-            const float p7 = fast_exp2(fmaf(__uint_as_float(sv[cch][2 * i + 7]), c, -mc));
-            l0 += p0 + p1;
-            l1 += p2 + p3;
-            l2 += p4 + p5;
-            l3 += p6 + p7;
+            float p0, p1, p2, p3, p4, p5, p6, p7;
+            f32x2_unpack(f32x2_fma(f32x2_pack(__uint_as_float(sv[cch][2 * i]), __uint_as_float(sv[cch][2 * i + 1])), c2, nmc2), p0, p1);
+            f32x2_unpack(f32x2_fma(f32x2_pack(__uint_as_float(sv[cch][2 * i + 2]), __uint_as_float(sv[cch][2 * i + 3])), c2, nmc2), p2, p3);
+            f32x2_unpack(f32x2_fma(f32x2_pack(__uint_as_float(sv[cch][2 * i + 4]), __uint_as_float(sv[cch][2 * i + 5])), c2, nmc2), p4, p5);
+            f32x2_unpack(f32x2_fma(f32x2_pack(__uint_as_float(sv[cch][2 * i + 6]), __uint_as_float(sv[cch][2 * i + 7])), c2, nmc2), p6, p7);
+            p0 = fast_exp2(p0); p1 = fast_exp2(p1); p2 = fast_exp2(p2); p3 = fast_exp2(p3);
+            p4 = fast_exp2(p4); p5 = fast_exp2(p5); p6 = fast_exp2(p6); p7 = fast_exp2(p7);
+            ls0 = f32x2_add(ls0, f32x2_pack(p0, p1));
+            ls1 = f32x2_add(ls1, f32x2_pack(p2, p3));
+            ls2 = f32x2_add(ls2, f32x2_pack(p4, p5));
+            ls3 = f32x2_add(ls3, f32x2_pack(p6, p7));
             pk[i] = pack_bf16(p0, p1);
             pk[i + 1] = pack_bf16(p2, p3);
             pk[i + 2] = pack_bf16(p4, p5);
             pk[i + 3] = pack_bf16(p6, p7);
           }
           tc::st_32x32b_x16(tmem_s + lane_base + cch * 16, pk);
+        }
+        float l0, l1, l2, l3;
+        {
+          float a0, a1;
+          f32x2_unpack(f32x2_add(f32x2_add(ls0, ls1), f32x2_add(ls2, ls3)), a0, a1);
+          l0 = a0; l1 = a1; l2 = 0.f; l3 = 0.f;
         }
         l += (l0 + l1) + (l2 + l3);
         CK(ck_exp);
@@ -438,47 +508,32 @@ prefill_attn_tc2_kernel(const PrefillParams p, const __grid_constant__ CUtensorM
           fence_proxy_async_smem();
         }
         tc::fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&bar_p_full[hx]);   // one arrival per warp
+        if (pend) {
+          // only at j == 0: the previous item's output leaves now; P of this tile is handed over inside
+          pend = false;
+          if (!t2_epilogue(p, tmem_o + lane_base, &bar_o_final[hx], n_final & 1, &bar_o_free[hx], &bar_p_full[hx], abort_flag,
+                           sStage + (warp - 4) * 2048, lane, quarter, hx, pend_inv, pend_q_row, pend_h, pend_tq0, pend_Lq)) {
+            ok = false;
+            break;
+          }
+          ++n_final;
+        } else {
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&bar_p_full[hx]);   // one arrival per warp
+        }
         CK(ck_sig);
         if (hx == 0 && r == 0 && j == nx - 1) PF_TRACE(n_item - 1, 7);
       }
       if (!ok) break;
       vt_base += n_all;
       if (nx > 0) {
-#ifdef B200_TRACE
-        ck_t0 = clock64();
-#endif
-        if (!mbar_wait(&bar_o_final[hx], n_final & 1, abort_flag)) break;
-        ++n_final;
-        if (hx == 0 && r == 0) PF_TRACE(n_item - 1, 8);
-        tc::fence_after_sync();
-        const float inv = l > 0.f ? 1.f / l : 0.f;
-        uint4* dst = reinterpret_cast<uint4*>(p.out + (static_cast<long long>(it.q_row + hx * QT + r / G) * p.H + it.h * G + r % G) * 128);
-        uint32_t ov[4][32];
-#pragma unroll
-        for (int cch = 0; cch < 4; ++cch) tc::ld_32x32b_x32(tmem_o + lane_base + cch * 32, ov[cch]);
-        tc::wait_ld();
-        // O is in registers: the accumulator may be overwritten by the next item already
-        tc::fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&bar_o_free[hx]);
-        if (row_ok) {
-#pragma unroll
-          for (int cch = 0; cch < 4; ++cch) {
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              uint4 w;
-              w.x = pack_bf16(__uint_as_float(ov[cch][8 * i]) * inv, __uint_as_float(ov[cch][8 * i + 1]) * inv);
-              w.y = pack_bf16(__uint_as_float(ov[cch][8 * i + 2]) * inv, __uint_as_float(ov[cch][8 * i + 3]) * inv);
-              w.z = pack_bf16(__uint_as_float(ov[cch][8 * i + 4]) * inv, __uint_as_float(ov[cch][8 * i + 5]) * inv);
-              w.w = pack_bf16(__uint_as_float(ov[cch][8 * i + 6]) * inv, __uint_as_float(ov[cch][8 * i + 7]) * inv);
-              dst[cch * 4 + i] = w;
-            }
-          }
-        }
-        CK(ck_epi);
-        if (hx == 0 && r == 0) PF_TRACE(n_item - 1, 9);
+        // (a pending epilogue was flushed at this item's first tile)
+        pend = true;
+        pend_inv = l > 0.f ? 1.f / l : 0.f;
+        pend_q_row = it.q_row;
+        pend_h = it.h;
+        pend_tq0 = it.tq0;
+        pend_Lq = it.Lq;
       } else if (row_ok) {
         // no visible key at all (Lk < Lq rows): zeros, as the reference's attention library does
         uint4* dst = reinterpret_cast<uint4*>(p.out + (static_cast<long long>(it.q_row + hx * QT + r / G) * p.H + it.h * G + r % G) * 128);
@@ -486,6 +541,9 @@ prefill_attn_tc2_kernel(const PrefillParams p, const __grid_constant__ CUtensorM
         for (int i = 0; i < 16; ++i) dst[i] = make_uint4(0, 0, 0, 0);
       }
     }
+    if (ok && pend)
+      t2_epilogue(p, tmem_o + lane_base, &bar_o_final[hx], n_final & 1, &bar_o_free[hx], nullptr, abort_flag,
+                  sStage + (warp - 4) * 2048, lane, quarter, hx, pend_inv, pend_q_row, pend_h, pend_tq0, pend_Lq);
 #ifdef B200_TRACE
     if (hx == 0 && r == 0 && blockIdx.x < 8) {
       unsigned long long* o = g_pf_trace + (blockIdx.x * kT2TraceItems + (kT2TraceItems - 1)) * kT2TraceSlots;
@@ -525,7 +583,7 @@ int read_status_prefill_tc2() {
 int launch_prefill_tc2(PrefillParams p, const CUtensorMap& map_q, const CUtensorMap& map_k, const CUtensorMap& map_v,
                        cudaStream_t stream) {
   p.n_slots = p.total_q / (2 * p.QT) + p.batch;
-  const size_t smem = 1024 + static_cast<size_t>(2 + 2 * kT2Ring) * kT2Tile +
+  const size_t smem = 1024 + static_cast<size_t>(2 + 2 * kT2Ring) * kT2Tile + 8 * 2048 +
                       (p.batch <= kT2MaxSeqSmem ? (p.batch + 1) * 4 : 4) + 64;
   static std::atomic<size_t> configured{0};
   if (configured.load() < smem) {
