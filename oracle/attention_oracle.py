@@ -78,24 +78,26 @@ def _gather_paged(cache, block_table_row, length, block_size):
 
 
 def _attend(q, k, v, scale, causal_offset):
-    """q (Lq,H,D), k/v (Lk,Hkv,D) -> (Lq,H,D) fp32.  Query row r sees keys <= r + causal_offset."""
+    """q (Lq,H,D), k/v (Lk,Hkv,D) -> (Lq,H,D) fp32.  Query row r sees keys <= r + causal_offset.
+    The G = H / Hkv query heads of a kv head are a separate axis, so K and V are never replicated."""
     lq, h, d = q.shape
     lk, hkv, _ = k.shape
     g = h // hkv
-    qf = q.float()
-    kf = k.float().repeat_interleave(g, dim=1)
-    vf = v.float().repeat_interleave(g, dim=1)
-    s = torch.einsum("qhd,khd->hqk", qf, kf) * scale
+    qf = q.float().view(lq, hkv, g, d)
+    kf = k.float()
+    vf = v.float()
+    s = torch.einsum("qhgd,khd->hgqk", qf, kf) * scale
     rows = torch.arange(lq).unsqueeze(1) + causal_offset
     cols = torch.arange(lk).unsqueeze(0)
     mask = cols > rows
-    s = s.masked_fill(mask.unsqueeze(0), float("-inf"))
+    if bool(mask.any()):
+        s = s.masked_fill(mask.view(1, 1, lq, lk), float("-inf"))
     m = s.amax(dim=-1, keepdim=True)
     m = torch.where(torch.isinf(m), torch.zeros_like(m), m)
     p = torch.exp(s - m)
     l = p.sum(dim=-1, keepdim=True)
     p = torch.where(l > 0, p / l.clamp_min(1e-38), torch.zeros_like(p))
-    return torch.einsum("hqk,khd->qhd", p, vf)
+    return torch.einsum("hgqk,khd->qhgd", p, vf).reshape(lq, h, d)
 
 
 def decode_attn_ref(q, k_cache, v_cache, context_lens, block_tables, scale):
