@@ -208,6 +208,55 @@ def test_decode_config2_shape_repeatable(b200):
     _status_ok()
 
 
+def test_decode_long_streams_dynamic_tail(b200):
+    """Large enough (>= 256 tiles per CTA) for the ticket-scheduled tail pieces: Qwen3-8B geometry at
+    TP2, batch 512, lengths U[512, 8192] (4.7 GB of cache).  The cache is built on the GPU; the oracle runs on a
+    sample of sequences whose blocks are copied back."""
+    pkg, _ = b200
+    h, hkv, d, bs = 16, 4, 128, 256
+    g = torch.Generator().manual_seed(91)
+    lens = torch.randint(512, 8193, (512,), generator=g, dtype=torch.int32)
+    bt, nb = make_block_tables(lens.tolist(), bs, g)
+    gd = torch.Generator(device=DEV).manual_seed(92)
+    kc = torch.randn(nb, bs, hkv, d, device=DEV, dtype=torch.bfloat16, generator=gd)
+    vc = torch.randn(nb, bs, hkv, d, device=DEV, dtype=torch.bfloat16, generator=gd)
+    q = torch.randn(512, h, d, device=DEV, dtype=torch.bfloat16, generator=gd)
+    tiles = int(((lens + 63) // 64).sum()) * hkv
+    assert tiles >= 256 * 2 * torch.cuda.get_device_properties(0).multi_processor_count, "not in the dynamic regime"
+    out1 = pkg.decode_attention(q, kc, vc, lens.to(DEV), bt.to(DEV), default_scale(d), hkv)
+    out2 = pkg.decode_attention(q, kc, vc, lens.to(DEV), bt.to(DEV), default_scale(d), hkv)
+    torch.cuda.synchronize()
+    assert torch.isfinite(out1.float()).all()
+    _close(out1, out2)                      # piece assignment differs from run to run; results agree
+    for i in list(range(0, 512, 47)) + [511]:
+        n = int(lens[i])
+        nblk = (n + bs - 1) // bs
+        idx = bt[i, :nblk].long().to(DEV)
+        k = kc[idx].reshape(-1, hkv, d)[:n].cpu()
+        v = vc[idx].reshape(-1, hkv, d)[:n].cpu()
+        small_bt = torch.arange(nblk, dtype=torch.int32).view(1, -1)
+        pad = nblk * bs - n
+        kcs = torch.cat([k, torch.zeros(pad, hkv, d, dtype=k.dtype)]).view(nblk, bs, hkv, d)
+        vcs = torch.cat([v, torch.zeros(pad, hkv, d, dtype=v.dtype)]).view(nblk, bs, hkv, d)
+        want = decode_attn_ref(q[i:i + 1].cpu(), kcs, vcs, lens[i:i + 1], small_bt, default_scale(d))
+        _close(out1[i:i + 1], want)
+    _status_ok()
+
+
+def test_decode_block_size_512(b200):
+    pkg, _ = b200
+    g = torch.Generator().manual_seed(93)
+    lens = [700, 512, 513, 1, 2000]
+    bt, nb = make_block_tables(lens, 512, g)
+    kc = (torch.randn(nb, 512, 2, 128, generator=g) * 0.5).to(torch.bfloat16)
+    vc = (torch.randn(nb, 512, 2, 128, generator=g) * 0.5).to(torch.bfloat16)
+    q = (torch.randn(len(lens), 4, 128, generator=g) * 0.5).to(torch.bfloat16)
+    cl = torch.tensor(lens, dtype=torch.int32)
+    out = pkg.decode_attention(q.to(DEV), kc.to(DEV), vc.to(DEV), cl.to(DEV), bt.to(DEV), default_scale(128), 2)
+    torch.cuda.synchronize()
+    _close(out, decode_attn_ref(q, kc, vc, cl, bt, default_scale(128)))
+
+
 def test_decode_cuda_graph_capture_replay(b200):
     """Capture with all-zero metadata in static buffers (nanovllm/engine/model_runner.py:215-250),
     replay with real metadata and padded rows (slot -1, len 0, stale table rows)."""
@@ -285,15 +334,15 @@ def _prefill_case(seed, lens, prefix, h, hkv, paged, poison=True):
     return q, kc, vc, cu_q, cu_k, bt, None
 
 
-VARIANTS = {"mma": 1, "tcgen05": 2, "tcgen05_persistent": 3}
+VARIANTS = {"mma": 1, "tcgen05": 2, "tcgen05_persistent": 3, "tcgen05_persistent_kv64": 4}
 
 
 def _variants(h, hkv):
     g = h // hkv
-    return ["mma"] + (["tcgen05", "tcgen05_persistent"] if 128 % g == 0 else [])
+    return ["mma"] + (["tcgen05", "tcgen05_persistent", "tcgen05_persistent_kv64"] if 128 % g == 0 else [])
 
 
-@pytest.mark.parametrize("variant", ["mma", "tcgen05", "tcgen05_persistent"])
+@pytest.mark.parametrize("variant", ["mma", "tcgen05", "tcgen05_persistent", "tcgen05_persistent_kv64"])
 @pytest.mark.parametrize("h,hkv", [(16, 8), (4, 1), (2, 2), (5, 1), (8, 1)])
 def test_prefill_dense_ragged(b200, h, hkv, variant):
     pkg, _ = b200
@@ -313,7 +362,7 @@ def test_prefill_dense_ragged(b200, h, hkv, variant):
     _status_ok()
 
 
-@pytest.mark.parametrize("variant", ["mma", "tcgen05", "tcgen05_persistent"])
+@pytest.mark.parametrize("variant", ["mma", "tcgen05", "tcgen05_persistent", "tcgen05_persistent_kv64"])
 @pytest.mark.parametrize("h,hkv", [(16, 8), (4, 1), (2, 2)])
 def test_prefill_paged_prefix_poisoned(b200, h, hkv, variant):
     pkg, _ = b200
@@ -328,6 +377,53 @@ def test_prefill_paged_prefix_poisoned(b200, h, hkv, variant):
     assert torch.isfinite(out.float()).all()
     _close(out, want)
     _status_ok()
+
+
+def test_prefill_config3_scale_and_many_sequences(b200):
+    """BASELINE config 3 at full size (256 sequences, U[100,1024]) against the oracle on a sample of
+    sequences, and a batch of more than 1024 short sequences (the slot table no longer fits in shared memory)."""
+    pkg, _ = b200
+    h, hkv, d = 16, 8, 128
+    for nseq, lo, hi, seed in ((256, 100, 1024, 3), (1500, 1, 40, 4)):
+        g = torch.Generator().manual_seed(seed)
+        lens = torch.randint(lo, hi + 1, (nseq,), generator=g, dtype=torch.int32)
+        cu = torch.zeros(nseq + 1, dtype=torch.int32)
+        cu[1:] = lens.cumsum(0)
+        t = int(cu[-1])
+        gd = torch.Generator(device=DEV).manual_seed(seed + 10)
+        q = torch.randn(t, h, d, device=DEV, dtype=torch.bfloat16, generator=gd)
+        k = torch.randn(t, hkv, d, device=DEV, dtype=torch.bfloat16, generator=gd)
+        v = torch.randn(t, hkv, d, device=DEV, dtype=torch.bfloat16, generator=gd)
+        mx = int(lens.max())
+        outs = {name: pkg.prefill_attention(q, k, v, cu.to(DEV), cu.to(DEV), mx, mx, default_scale(d), hkv, kernel_variant=var)
+                for name, var in VARIANTS.items()}
+        torch.cuda.synchronize()
+        for i in list(range(0, nseq, max(1, nseq // 12))) + [nseq - 1]:
+            a, b_ = int(cu[i]), int(cu[i + 1])
+            one = torch.tensor([0, b_ - a], dtype=torch.int32)
+            want = prefill_attn_ref(q[a:b_].cpu(), k[a:b_].cpu(), v[a:b_].cpu(), one, one, default_scale(d))
+            for name, out in outs.items():
+                _close(out[a:b_], want)
+    _status_ok()
+
+
+def test_prefill_paged_block_size_512(b200):
+    pkg, _ = b200
+    g = torch.Generator().manual_seed(95)
+    lens, prefix = [900, 513, 100], [512, 0, 0]
+    lq = [a - b_ for a, b_ in zip(lens, prefix)]
+    cu_q = torch.tensor([0] + lq).cumsum(0).to(torch.int32)
+    cu_k = torch.tensor([0] + lens).cumsum(0).to(torch.int32)
+    bt, nb = make_block_tables(lens, 512, g)
+    kc = torch.randn(nb, 512, 2, 128, generator=g).to(torch.bfloat16)
+    vc = torch.randn(nb, 512, 2, 128, generator=g).to(torch.bfloat16)
+    q = torch.randn(sum(lq), 4, 128, generator=g).to(torch.bfloat16)
+    want = prefill_attn_ref(q, kc, vc, cu_q, cu_k, default_scale(128), bt)
+    for name, var in VARIANTS.items():
+        out = pkg.prefill_attention(q.to(DEV), kc.to(DEV), vc.to(DEV), cu_q.to(DEV), cu_k.to(DEV), max(lq), max(lens),
+                                    default_scale(128), 2, block_tables=bt.to(DEV), kernel_variant=var)
+        torch.cuda.synchronize()
+        _close(out, want)
 
 
 def test_prefill_module_store_then_attend(b200):
