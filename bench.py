@@ -40,6 +40,9 @@ WORKLOADS = {
     "decode_cfg2": dict(kind="decode", H=16, Hkv=8, D=128, batch=256, lo=100, hi=2048, seed=2, layers=8),
     "decode_cfg4": dict(kind="decode", H=32, Hkv=8, D=128, batch=512, lo=512, hi=8192, seed=4, layers=3),
     "prefill_cfg3": dict(kind="prefill", H=16, Hkv=8, D=128, batch=256, lo=100, hi=1024, seed=3),
+    # the same batch with a prefix-cache hit (a random whole number of blocks) on the second half of the
+    # sequences: the whole batch then reads K/V from the paged cache through block tables
+    "prefill_cfg3_prefix": dict(kind="prefill", H=16, Hkv=8, D=128, batch=256, lo=100, hi=1024, seed=3, prefix=True),
 }
 BLOCK = 256
 
@@ -304,9 +307,13 @@ def run_reference(args, w, rank, world):
         return None
     if w["kind"] != "decode":
         raise SystemExit("--impl reference supports the decode workloads")
-    sample = 64
-    for _ in range(min(args.warmup, 1)):
-        cpu_decode_baseline(w, sample=8)
+    # a step = the decode attention of the first `sample` sequences of the workload; the sample is sized
+    # from a short probe so that the K timed steps take about 40 s in total on this host
+    probe = cpu_decode_baseline(w, sample=8)
+    per_seq = probe["seconds_per_pass"] / 8
+    sample = int(max(2, min(w["batch"], 40.0 / max(args.steps, 1) / max(per_seq, 1e-6))))
+    for _ in range(min(args.warmup, 2)):
+        cpu_decode_baseline(w, sample=min(sample, 8))
     res = cpu_decode_baseline(w, sample=sample, repeats=args.steps)
     ms = res["seconds_per_pass"] * 1e3
     return {
@@ -338,13 +345,44 @@ def prefill_inputs(dev, w=None):
     return w, lens, cu.to(dev), q, k, v
 
 
-def secondary_prefill(dev, iters=10):
+def prefill_prefix_inputs(dev, w):
+    """Paged form: every key comes from the cache; the second half of the batch has a cached prefix."""
+    from oracle.attention_oracle import make_block_tables
+    lens, g = seeded_lens(w)
+    n = w["batch"]
+    prefix = torch.zeros(n, dtype=torch.int32)
+    for i in range(n // 2, n):
+        mxb = (int(lens[i]) - 1) // BLOCK
+        prefix[i] = BLOCK * int(torch.randint(0, mxb + 1, (1,), generator=g)) if mxb > 0 else 0
+    lq = lens - prefix
+    cu_q = torch.zeros(n + 1, dtype=torch.int32)
+    cu_q[1:] = lq.cumsum(0)
+    cu_k = torch.zeros(n + 1, dtype=torch.int32)
+    cu_k[1:] = lens.cumsum(0)
+    bt, nb = make_block_tables(lens.tolist(), BLOCK, g)
+    gd = torch.Generator(device=dev).manual_seed(78)
+    q = torch.randn(int(cu_q[-1]), w["H"], w["D"], device=dev, dtype=torch.bfloat16, generator=gd)
+    kc = torch.randn(nb, BLOCK, w["Hkv"], w["D"], device=dev, dtype=torch.bfloat16, generator=gd)
+    vc = torch.randn(nb, BLOCK, w["Hkv"], w["D"], device=dev, dtype=torch.bfloat16, generator=gd)
+    return lq, lens, cu_q.to(dev), cu_k.to(dev), bt.to(dev), q, kc, vc
+
+
+def secondary_prefill(dev, iters=10, workload="prefill_cfg3"):
     import nanovllm_b200
     from oracle.attention_oracle import prefill_algorithmic_flops
-    w, lens, cu, q, k, v = prefill_inputs(dev)
-    flops = prefill_algorithmic_flops(lens.tolist(), lens.tolist(), w["H"], w["D"])
-    mx = int(lens.max())
-    f = lambda: nanovllm_b200.prefill_attention(q, k, v, cu, cu, mx, mx, w["D"] ** -0.5, w["Hkv"])
+    w = WORKLOADS[workload]
+    if w.get("prefix"):
+        lq, lens, cu_q, cu_k, bt, q, kc, vc = prefill_prefix_inputs(dev, w)
+        flops = prefill_algorithmic_flops(lq.tolist(), lens.tolist(), w["H"], w["D"])
+        f = lambda: nanovllm_b200.prefill_attention(q, kc, vc, cu_q, cu_k, int(lq.max()), int(lens.max()), w["D"] ** -0.5,
+                                                    w["Hkv"], block_tables=bt)
+        label = "prefill_cfg3_prefix (256 seqs, len uniform[100,1024], second half with a cached whole-block prefix, paged K/V)"
+    else:
+        w, lens, cu, q, k, v = prefill_inputs(dev, w)
+        flops = prefill_algorithmic_flops(lens.tolist(), lens.tolist(), w["H"], w["D"])
+        mx = int(lens.max())
+        f = lambda: nanovllm_b200.prefill_attention(q, k, v, cu, cu, mx, mx, w["D"] ** -0.5, w["Hkv"])
+        label = "prefill_cfg3 (256 seqs, len uniform[100,1024], dense K/V, causal)"
     for _ in range(3):
         f()
     torch.cuda.synchronize()
@@ -357,7 +395,7 @@ def secondary_prefill(dev, iters=10):
     ms = a.elapsed_time(b) / iters
     pk = peaks()
     tf = flops / (ms * 1e-3) / 1e12
-    return {"metric": "prefill_attn_tflops", "workload": "prefill_cfg3 (256 seqs, len uniform[100,1024], dense K/V, causal)",
+    return {"metric": "prefill_attn_tflops", "workload": label,
             "value": round(tf, 1), "unit": "TFLOP/s", "ms": round(ms, 4), "flops": flops,
             "frac_of_bf16_peak": round(tf / pk["bf16"], 4), "peak": pk["bf16"], "peak_source": pk["source"],
             "frac_of_spec_2250": round(tf / 2250.0, 4)}
@@ -365,10 +403,10 @@ def secondary_prefill(dev, iters=10):
 
 def run_prefill(args, w, rank, world, local):
     if world != 1:
-        raise SystemExit("prefill_cfg3 is a single-GPU workload")
+        raise SystemExit("the prefill workloads are single-GPU workloads")
     dev = torch.device("cuda", local)
     torch.cuda.set_device(dev)
-    s = secondary_prefill(dev, iters=args.steps)
+    s = secondary_prefill(dev, iters=args.steps, workload=args.workload)
     return {"metric": s["metric"], "value": s["value"], "unit": s["unit"], "n_gpus": 1, "steps": args.steps,
             "warmup": 3, "ms_per_step": s["ms"], "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic", "config": {"workload": s["workload"]},
@@ -379,7 +417,7 @@ def run_prefill(args, w, rank, world, local):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--steps", type=int, default=1000)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="decode_cfg2", choices=list(WORKLOADS))
