@@ -29,7 +29,7 @@ extern std::atomic<long long> g_launches;
 constexpr int kT2Kv = 128;
 constexpr int kT2Sub = 128 * 128;            // one 64-column sub-tile of a 128-row tile (bytes)
 constexpr int kT2Tile = 2 * kT2Sub;          // 128 rows x 128 dims bf16 = 32 KiB
-constexpr int kT2Threads = 384;   // warpgroup 0: TMA producer, MMA issuer, two idle warps; warpgroups 1, 2: softmax
+constexpr int kT2Threads = 512;   // warpgroup 0: TMA producer, MMA issuer, two idle warps; 1, 2: softmax; 3: output
 constexpr int kT2Ring = 2;                   // K ring depth and V ring depth
 constexpr int kT2Items = 4;                  // item descriptors in flight
 constexpr int kT2MaxSeqSmem = 1024;          // sequences whose slot table fits in shared memory
@@ -64,55 +64,49 @@ struct T2Item {
   int n[2];       // K/V tiles each half needs (n[1] == 0: half B is empty)
 };
 
-// Output of one half of an item: read the finished O row out of TMEM, release the accumulator
-// (and, if given, hand the first P of the next item to the issuer), then scale by 1 / row sum and
-// store bf16 rows through a per-warp staging tile so that every store instruction writes 64-byte
-// row segments (a thread owns a whole row: stored directly, each instruction would touch 32
-// different lines with 16 bytes each).
-__device__ __forceinline__ bool t2_epilogue(const PrefillParams& p, uint32_t tmem_o_lane, uint64_t* bar_o_final,
-                                            uint32_t parity, uint64_t* bar_o_free, uint64_t* bar_p_full,
-                                            volatile int* abort_flag, unsigned char* stage, int lane, int quarter, int hx,
-                                            float inv, int q_row, int h, int tq0, int Lq) {
-  if (!mbar_wait(bar_o_final, parity, abort_flag)) return false;
-  tc::fence_after_sync();
-  uint32_t ov[4][32];
-#pragma unroll
-  for (int cch = 0; cch < 4; ++cch) tc::ld_32x32b_x32(tmem_o_lane + cch * 32, ov[cch]);
-  tc::wait_ld();
-  tc::fence_before_sync();
-  __syncwarp();
-  if (lane == 0) {
-    mbar_arrive(bar_o_free);
-    if (bar_p_full) mbar_arrive(bar_p_full);
-  }
+// Output of one half of an item, run by the output warpgroup: read the finished O row out of TMEM
+// in 32-column chunks, scale by 1 / row sum and store bf16 rows through a per-warp staging tile so
+// that every store instruction writes 64-byte row segments (a thread owns a whole row: stored
+// directly, each instruction would touch 32 different lines with 16 bytes each).  The accumulator
+// is released as soon as its last chunk is in registers.
+__device__ __forceinline__ void t2_output(const PrefillParams& p, uint32_t tmem_o_lane, uint64_t* bar_o_free,
+                                          unsigned char* stage, int lane, int quarter, int hx,
+                                          float inv, int q_row, int h, int tq0, int Lq) {
   const int G = p.G, QT = p.QT;
-  const int srow = (lane >> 2), sq = lane & 3;           // read-back role: 8 rows x 4 chunks per instruction
+  const int srow = lane >> 1, sq = lane & 1;             // read-back role: 16 rows x 2 chunks per instruction
+#pragma unroll 1
+  for (int cch = 0; cch < 8; ++cch) {
+    uint32_t ov[16];
+    tc::ld_32x32b_x16(tmem_o_lane + cch * 16, ov);
+    tc::wait_ld();
+    if (cch == 7) {
+      tc::fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_o_free);
+    }
 #pragma unroll
-  for (int cch = 0; cch < 4; ++cch) {
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
+    for (int i = 0; i < 2; ++i) {
       uint4 w;
-      w.x = pack_bf16(__uint_as_float(ov[cch][8 * i]) * inv, __uint_as_float(ov[cch][8 * i + 1]) * inv);
-      w.y = pack_bf16(__uint_as_float(ov[cch][8 * i + 2]) * inv, __uint_as_float(ov[cch][8 * i + 3]) * inv);
-      w.z = pack_bf16(__uint_as_float(ov[cch][8 * i + 4]) * inv, __uint_as_float(ov[cch][8 * i + 5]) * inv);
-      w.w = pack_bf16(__uint_as_float(ov[cch][8 * i + 6]) * inv, __uint_as_float(ov[cch][8 * i + 7]) * inv);
-      *reinterpret_cast<uint4*>(stage + lane * 64 + ((i ^ ((lane >> 1) & 3)) << 4)) = w;
+      w.x = pack_bf16(__uint_as_float(ov[8 * i]) * inv, __uint_as_float(ov[8 * i + 1]) * inv);
+      w.y = pack_bf16(__uint_as_float(ov[8 * i + 2]) * inv, __uint_as_float(ov[8 * i + 3]) * inv);
+      w.z = pack_bf16(__uint_as_float(ov[8 * i + 4]) * inv, __uint_as_float(ov[8 * i + 5]) * inv);
+      w.w = pack_bf16(__uint_as_float(ov[8 * i + 6]) * inv, __uint_as_float(ov[8 * i + 7]) * inv);
+      *reinterpret_cast<uint4*>(stage + lane * 32 + ((i ^ ((lane >> 2) & 1)) << 4)) = w;
     }
     __syncwarp();
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      const int lr = 8 * k + srow;                          // row within the warp's 32
-      const uint4 w = *reinterpret_cast<const uint4*>(stage + lr * 64 + ((sq ^ ((lr >> 1) & 3)) << 4));
+    for (int k = 0; k < 2; ++k) {
+      const int lr = 16 * k + srow;                         // row within the warp's 32
+      const uint4 w = *reinterpret_cast<const uint4*>(stage + lr * 32 + ((sq ^ ((lr >> 2) & 1)) << 4));
       const int rr = quarter * 32 + lr;                     // row of the 128-row tile
       const int tk = tq0 + hx * QT + rr / G;
       if (rr < QT * G && tk < Lq)
         *reinterpret_cast<uint4*>(reinterpret_cast<unsigned char*>(
             p.out + (static_cast<long long>(q_row + hx * QT + rr / G) * p.H + h * G + rr % G) * 128) +
-            cch * 64 + sq * 16) = w;
+            cch * 32 + sq * 16) = w;
     }
     __syncwarp();
   }
-  return true;
 }
 
 __global__ void __launch_bounds__(kT2Threads, 1)
@@ -129,6 +123,8 @@ prefill_attn_tc2_kernel(const PrefillParams p, const __grid_constant__ CUtensorM
   __shared__ __align__(8) uint64_t bar_q_full[2], bar_q_empty[2];
   __shared__ __align__(8) uint64_t bar_k_full[kT2Ring], bar_k_empty[kT2Ring], bar_v_full[kT2Ring], bar_v_empty[kT2Ring];
   __shared__ __align__(8) uint64_t bar_s_full[2], bar_p_full[2], bar_o_final[2], bar_o_free[2];
+  __shared__ __align__(8) uint64_t bar_l_full[2], bar_l_empty[2];
+  __shared__ float s_inv[2][128];                        // 1 / row sum of a finished half, softmax -> output warpgroup
   __shared__ __align__(16) T2Item s_item[kT2Items];
   __shared__ uint32_t s_tmem_base;
   __shared__ int s_abort;
@@ -139,7 +135,7 @@ prefill_attn_tc2_kernel(const PrefillParams p, const __grid_constant__ CUtensorM
 
   if (tid == 0) {
     s_abort = 0;
-    for (int i = 0; i < kT2Items; ++i) { mbar_init(&bar_item_full[i], 1); mbar_init(&bar_item_empty[i], 9); }
+    for (int i = 0; i < kT2Items; ++i) { mbar_init(&bar_item_full[i], 1); mbar_init(&bar_item_empty[i], 13); }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&bar_q_full[i], 1);
       mbar_init(&bar_q_empty[i], 1);
@@ -147,6 +143,8 @@ prefill_attn_tc2_kernel(const PrefillParams p, const __grid_constant__ CUtensorM
       mbar_init(&bar_p_full[i], 4);
       mbar_init(&bar_o_final[i], 1);
       mbar_init(&bar_o_free[i], 4);
+      mbar_init(&bar_l_full[i], 4);
+      mbar_init(&bar_l_empty[i], 4);
     }
     for (int i = 0; i < kT2Ring; ++i) {
       mbar_init(&bar_k_full[i], 1);
@@ -171,7 +169,7 @@ prefill_attn_tc2_kernel(const PrefillParams p, const __grid_constant__ CUtensorM
   // Registers move from the light warpgroup to the two softmax warpgroups, which hold a whole
   // 128-column S row (and later the O row) per thread.
   if (warp < 4) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 88;" ::: "memory");
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 80;" ::: "memory");
   if (warp == 0) {
     // ================================ TMA producer ================================
     if (lane == 0) {
@@ -186,10 +184,13 @@ prefill_attn_tc2_kernel(const PrefillParams p, const __grid_constant__ CUtensorM
         // a ticket; each CTA draws until it fails, the last ticket of the launch resets the counter
         const unsigned int tk = atomicAdd(&g_prefill_ticket, 1u);
         if (tk == n_items + gridDim.x - 1) atomicExch(&g_prefill_ticket, 0u);
-        T2Item it;
-        it.seq = -1;
+        // the descriptor is built in its ring slot; only what the loads need stays in registers
+        const int is = n_pub % kT2Items;
+        if (!mbar_wait(&bar_item_empty[is], ((n_pub / kT2Items) & 1) ^ 1, abort_flag)) { ok = false; break; }
+        int seq = -1, h = 0, q_row = 0, k_begin = 0, n = 0;
+        bool b_rows = false;                                            // half B holds query rows
         if (tk < n_items) {
-          const int h = tk % p.Hkv;
+          h = tk % p.Hkv;
           const int x = p.n_slots - 1 - static_cast<int>(tk / p.Hkv);   // later (heavier) blocks first
           int lo = 0, hi = p.batch;
           while (hi - lo > 1) {
@@ -197,48 +198,48 @@ prefill_attn_tc2_kernel(const PrefillParams p, const __grid_constant__ CUtensorM
             const int f = slot_in_smem ? s_slot[mid] : __ldg(p.cu_q + mid) / QB + mid;
             if (f <= x) lo = mid; else hi = mid;
           }
-          const int q_begin = __ldg(p.cu_q + lo), q_end = __ldg(p.cu_q + lo + 1);
-          const int Lq = q_end - q_begin;
+          const int q_begin = __ldg(p.cu_q + lo);
+          const int Lq = __ldg(p.cu_q + lo + 1) - q_begin;
           const int qb = x - (q_begin / QB + lo);
           if (qb < 0 || qb * QB >= Lq) continue;                        // slot owns no query block
-          const int k_begin = __ldg(p.cu_k + lo);
+          k_begin = __ldg(p.cu_k + lo);
           const int Lk = __ldg(p.cu_k + lo + 1) - k_begin;
           const int shift = Lk - Lq;
           const int tq0 = qb * QB;
-          const int endA = min(tq0 + QT, Lq), endB = min(tq0 + QB, Lq);
-          it.seq = lo;
-          it.h = h;
-          it.q_row = q_begin + tq0;
-          it.tq0 = tq0;
-          it.Lq = Lq;
-          it.Lk = Lk;
-          it.k_begin = k_begin;
-          it.n[0] = max(0, (min(Lk, shift + endA) + kT2Kv - 1) / kT2Kv);
-          it.n[1] = tq0 + QT < Lq ? max(0, (min(Lk, shift + endB) + kT2Kv - 1) / kT2Kv) : 0;
+          const int nA = max(0, (min(Lk, shift + min(tq0 + QT, Lq)) + kT2Kv - 1) / kT2Kv);
+          b_rows = tq0 + QT < Lq;
+          const int nB = b_rows ? max(0, (min(Lk, shift + min(tq0 + QB, Lq)) + kT2Kv - 1) / kT2Kv) : 0;
+          seq = lo;
+          q_row = q_begin + tq0;
+          n = max(nA, nB);
+          s_item[is].h = h;
+          s_item[is].q_row = q_row;
+          s_item[is].tq0 = tq0;
+          s_item[is].Lq = Lq;
+          s_item[is].Lk = Lk;
+          s_item[is].k_begin = k_begin;
+          s_item[is].n[0] = nA;
+          s_item[is].n[1] = nB;
+          PF_TRACE(n_pub, 11, (static_cast<unsigned long long>(nA) << 8) | nB | (1ull << 32));
         }
-        // publish (an item, or the end marker)
-        const int is = n_pub % kT2Items;
-        if (!mbar_wait(&bar_item_empty[is], ((n_pub / kT2Items) & 1) ^ 1, abort_flag)) { ok = false; break; }
-        s_item[is] = it;
-        mbar_arrive(&bar_item_full[is]);
-        if (it.seq < 0) break;
+        s_item[is].seq = seq;
+        mbar_arrive(&bar_item_full[is]);                                // an item, or the end marker
+        if (seq < 0) break;
         PF_TRACE(n_pub, 0);
-        PF_TRACE(n_pub, 11, (static_cast<unsigned long long>(it.n[0]) << 8) | it.n[1] | (1ull << 32));
         // Q tiles (the buffers are free once every S MMA of the previous item has completed)
         const uint32_t qph = (n_pub & 1) ^ 1;
         for (int hx = 0; hx < 2; ++hx) {
           if (!mbar_wait(&bar_q_empty[hx], qph, abort_flag)) { ok = false; break; }
-          if (hx == 1 && it.n[1] == 0 && it.tq0 + QT >= it.Lq) { mbar_arrive(&bar_q_full[1]); continue; }
+          if (hx == 1 && !b_rows) { mbar_arrive(&bar_q_full[1]); continue; }
           mbar_expect_tx(&bar_q_full[hx], kT2Tile);
-          tma_load_3d(sQ + hx * kT2Tile, &map_q, &bar_q_full[hx], 0, it.h * G, it.q_row + hx * QT);
-          tma_load_3d(sQ + hx * kT2Tile + kT2Sub, &map_q, &bar_q_full[hx], 64, it.h * G, it.q_row + hx * QT);
+          tma_load_3d(sQ + hx * kT2Tile, &map_q, &bar_q_full[hx], 0, h * G, q_row + hx * QT);
+          tma_load_3d(sQ + hx * kT2Tile + kT2Sub, &map_q, &bar_q_full[hx], 64, h * G, q_row + hx * QT);
         }
         if (!ok) break;
         PF_TRACE(n_pub, 1);
         ++n_pub;
         // K and V tiles
-        const int n = max(it.n[0], it.n[1]);
-        const int* bt_row = p.block_tables ? p.block_tables + it.seq * p.bt_row_stride : nullptr;
+        const int* bt_row = p.block_tables ? p.block_tables + seq * p.bt_row_stride : nullptr;
         for (int j = 0; j < n; ++j) {
           int row0;
           if (bt_row) {
@@ -248,19 +249,19 @@ prefill_attn_tc2_kernel(const PrefillParams p, const __grid_constant__ CUtensorM
             row0 = (blk >= 0 && blk < p.num_blocks) ? static_cast<int>(blk * p.block_size + (tok0 - col * p.block_size))
                                                     : -kT2Kv;
           } else {
-            row0 = it.k_begin + j * kT2Kv;
+            row0 = k_begin + j * kT2Kv;
           }
           const int ks = kt % kT2Ring;
           if (!mbar_wait(&bar_k_empty[ks], ((kt / kT2Ring) & 1) ^ 1, abort_flag)) { ok = false; break; }
           mbar_expect_tx(&bar_k_full[ks], kT2Tile);
-          tma_load_3d(sK + ks * kT2Tile, &map_k, &bar_k_full[ks], 0, it.h, row0);
-          tma_load_3d(sK + ks * kT2Tile + kT2Sub, &map_k, &bar_k_full[ks], 64, it.h, row0);
+          tma_load_3d(sK + ks * kT2Tile, &map_k, &bar_k_full[ks], 0, h, row0);
+          tma_load_3d(sK + ks * kT2Tile + kT2Sub, &map_k, &bar_k_full[ks], 64, h, row0);
           ++kt;
           const int vs = vt % kT2Ring;
           if (!mbar_wait(&bar_v_empty[vs], ((vt / kT2Ring) & 1) ^ 1, abort_flag)) { ok = false; break; }
           mbar_expect_tx(&bar_v_full[vs], kT2Tile);
-          tma_load_3d(sV + vs * kT2Tile, &map_v, &bar_v_full[vs], 0, it.h, row0);
-          tma_load_3d(sV + vs * kT2Tile + kT2Sub, &map_v, &bar_v_full[vs], 64, it.h, row0);
+          tma_load_3d(sV + vs * kT2Tile, &map_v, &bar_v_full[vs], 0, h, row0);
+          tma_load_3d(sV + vs * kT2Tile + kT2Sub, &map_v, &bar_v_full[vs], 64, h, row0);
           ++vt;
         }
       }
@@ -270,7 +271,9 @@ prefill_attn_tc2_kernel(const PrefillParams p, const __grid_constant__ CUtensorM
     if (lane == 0) {
       constexpr uint32_t idesc_qk = tc::idesc_bf16_f32(128, 128, false, false);
       constexpr uint32_t idesc_pv = tc::idesc_bf16_f32(128, 128, false, true);
-      const uint32_t q_addr = smem_u32(sQ), k_addr = smem_u32(sK), v_addr = smem_u32(sV);
+      constexpr uint32_t desc_hi = tc::smem_desc_sw128_hi(1024);
+      const uint32_t q_lo = tc::smem_desc_sw128_lo(smem_u32(sQ), 16), k_lo = tc::smem_desc_sw128_lo(smem_u32(sK), 16);
+      const uint32_t v_lo = tc::smem_desc_sw128_lo(smem_u32(sV), kT2Sub);
       int n_item = 0, kt = 0, vt = 0;
       int np[2] = {0, 0};     // P tiles consumed per half (phase of bar_p_full)
       int no[2] = {0, 0};     // items whose O was read out per half (phase of bar_o_free)
@@ -278,26 +281,25 @@ prefill_attn_tc2_kernel(const PrefillParams p, const __grid_constant__ CUtensorM
       auto issue_s = [&](int hx, int kslot) {
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
-          const uint32_t off = (ks >> 2) * kT2Sub + (ks & 3) * 32;
-          tc::mma_ss(tmem + hx * 128, tc::smem_desc_sw128(q_addr + hx * kT2Tile + off, 16, 1024),
-                     tc::smem_desc_sw128(k_addr + kslot * kT2Tile + off, 16, 1024), idesc_qk, ks > 0);
+          const uint32_t off = ((ks >> 2) * kT2Sub + (ks & 3) * 32) >> 4;
+          tc::mma_ss_lo(tmem + hx * 128, q_lo + hx * (kT2Tile >> 4) + off, k_lo + kslot * (kT2Tile >> 4) + off, desc_hi,
+                        idesc_qk, ks > 0);
         }
         tc::commit(&bar_s_full[hx]);
       };
       auto issue_pv = [&](int hx, int vslot, bool accumulate) {
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks)
-          tc::mma_ts(tmem + 256 + hx * 128, tmem + hx * 128 + ks * 8,
-                     tc::smem_desc_sw128(v_addr + vslot * kT2Tile + ks * 2048, kT2Sub, 1024), idesc_pv, accumulate || ks > 0);
+          tc::mma_ts_lo(tmem + 256 + hx * 128, tmem + hx * 128 + ks * 8, v_lo + vslot * (kT2Tile >> 4) + ks * (2048 >> 4),
+                        desc_hi, idesc_pv, accumulate || ks > 0);
       };
       while (ok) {
         const int is = n_item % kT2Items;
         if (!mbar_wait(&bar_item_full[is], (n_item / kT2Items) & 1, abort_flag)) break;
-        const T2Item it = s_item[is];
+        const int seq = s_item[is].seq, nA = s_item[is].n[0], nB = s_item[is].n[1], n = max(nA, nB);
         mbar_arrive(&bar_item_empty[is]);
-        if (it.seq < 0) break;
+        if (seq < 0) break;
         PF_TRACE(n_item, 2);
-        const int nA = it.n[0], nB = it.n[1], n = max(nA, nB);
         const uint32_t qph = n_item & 1;
         if (!mbar_wait(&bar_q_full[0], qph, abort_flag) || !mbar_wait(&bar_q_full[1], qph, abort_flag)) break;
         PF_TRACE(n_item, 3);
@@ -349,8 +351,8 @@ prefill_attn_tc2_kernel(const PrefillParams p, const __grid_constant__ CUtensorM
       }
     }
   }
-  } else {
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 208;" ::: "memory");
+  } else if (warp < 12) {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 192;" ::: "memory");
     // ================================ softmax / epilogue ================================
     const int hx = (warp - 4) >> 2;                     // which half this warpgroup serves
     const int quarter = warp & 3;                       // TMEM lanes this warp may touch
@@ -360,12 +362,7 @@ prefill_attn_tc2_kernel(const PrefillParams p, const __grid_constant__ CUtensorM
     const float c = p.scale_log2;
     int n_item = 0, ns = 0, n_final = 0, vt_base = 0;
     bool ok = true;
-    // The output of an item leaves one step late: its O row is read out of TMEM right before the
-    // first P of the NEXT item is handed to the issuer, and converted / stored while the tensor
-    // core runs that item's first PV, instead of stalling this warpgroup at the item boundary.
-    bool pend = false;
-    float pend_inv = 0.f;
-    int pend_q_row = 0, pend_h = 0, pend_tq0 = 0, pend_Lq = 0;
+    int n_fin = 0;                                      // halves handed to the output warpgroup
 
 #ifdef B200_TRACE
     long long ck_wait = 0, ck_ld = 0, ck_max = 0, ck_exp = 0, ck_sig = 0, ck_epi = 0, ck_tiles = 0, ck_t0 = 0;
@@ -381,7 +378,7 @@ prefill_attn_tc2_kernel(const PrefillParams p, const __grid_constant__ CUtensorM
       if (lane == 0) mbar_arrive(&bar_item_empty[is]);   // this warp has its copy
       if (it.seq < 0) break;
       ++n_item;
-      const int nx = it.n[hx];
+      const int nx = hx ? it.n[1] : it.n[0];
       const int n_all = max(it.n[0], it.n[1]);
       const int shift = it.Lk - it.Lq;
       const int tok = it.tq0 + hx * QT + r / G;
@@ -444,13 +441,13 @@ prefill_attn_tc2_kernel(const PrefillParams p, const __grid_constant__ CUtensorM
             const float alpha = grow ? fast_exp2((m_used - m_new) * c) : 1.f;
             if (grow) { m_used = m_new; l *= alpha; }
 #pragma unroll
-            for (int cch = 0; cch < 4; ++cch) {
-              uint32_t v[32];
-              tc::ld_32x32b_x32(tmem_o + lane_base + cch * 32, v);
+            for (int cch = 0; cch < 8; ++cch) {
+              uint32_t v[16];
+              tc::ld_32x32b_x16(tmem_o + lane_base + cch * 16, v);
               tc::wait_ld();
 #pragma unroll
-              for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
-              tc::st_32x32b_x32(tmem_o + lane_base + cch * 32, v);
+              for (int i = 0; i < 16; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+              tc::st_32x32b_x16(tmem_o + lane_base + cch * 16, v);
             }
           }
         }
@@ -508,32 +505,20 @@ prefill_attn_tc2_kernel(const PrefillParams p, const __grid_constant__ CUtensorM
           fence_proxy_async_smem();
         }
         tc::fence_before_sync();
-        if (pend) {
-          // only at j == 0: the previous item's output leaves now; P of this tile is handed over inside
-          pend = false;
-          if (!t2_epilogue(p, tmem_o + lane_base, &bar_o_final[hx], n_final & 1, &bar_o_free[hx], &bar_p_full[hx], abort_flag,
-                           sStage + (warp - 4) * 2048, lane, quarter, hx, pend_inv, pend_q_row, pend_h, pend_tq0, pend_Lq)) {
-            ok = false;
-            break;
-          }
-          ++n_final;
-        } else {
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&bar_p_full[hx]);   // one arrival per warp
-        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bar_p_full[hx]);   // one arrival per warp
         CK(ck_sig);
         if (hx == 0 && r == 0 && j == nx - 1) PF_TRACE(n_item - 1, 7);
       }
       if (!ok) break;
       vt_base += n_all;
       if (nx > 0) {
-        // (a pending epilogue was flushed at this item's first tile)
-        pend = true;
-        pend_inv = l > 0.f ? 1.f / l : 0.f;
-        pend_q_row = it.q_row;
-        pend_h = it.h;
-        pend_tq0 = it.tq0;
-        pend_Lq = it.Lq;
+        // the row's 1 / sum goes to the output warpgroup, which drains O while this one moves on
+        if (!mbar_wait(&bar_l_empty[hx], (n_fin & 1) ^ 1, abort_flag)) { ok = false; break; }
+        s_inv[hx][r] = l > 0.f ? 1.f / l : 0.f;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bar_l_full[hx]);
+        ++n_fin;
       } else if (row_ok) {
         // no visible key at all (Lk < Lq rows): zeros, as the reference's attention library does
         uint4* dst = reinterpret_cast<uint4*>(p.out + (static_cast<long long>(it.q_row + hx * QT + r / G) * p.H + it.h * G + r % G) * 128);
@@ -541,15 +526,45 @@ prefill_attn_tc2_kernel(const PrefillParams p, const __grid_constant__ CUtensorM
         for (int i = 0; i < 16; ++i) dst[i] = make_uint4(0, 0, 0, 0);
       }
     }
-    if (ok && pend)
-      t2_epilogue(p, tmem_o + lane_base, &bar_o_final[hx], n_final & 1, &bar_o_free[hx], nullptr, abort_flag,
-                  sStage + (warp - 4) * 2048, lane, quarter, hx, pend_inv, pend_q_row, pend_h, pend_tq0, pend_Lq);
 #ifdef B200_TRACE
     if (hx == 0 && r == 0 && blockIdx.x < 8) {
       unsigned long long* o = g_pf_trace + (blockIdx.x * kT2TraceItems + (kT2TraceItems - 1)) * kT2TraceSlots;
       o[0] = ck_tiles; o[1] = ck_wait; o[2] = ck_ld; o[3] = ck_max; o[4] = ck_exp; o[5] = ck_sig; o[6] = ck_epi; o[7] = n_item;
     }
 #endif
+  } else {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 48;" ::: "memory");
+    // ================================ output warpgroup ================================
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;
+    const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
+    int n_item = 0;
+    int nf[2] = {0, 0};                                  // halves drained so far
+    bool ok = true;
+    while (ok) {
+      const int is = n_item % kT2Items;
+      if (!mbar_wait(&bar_item_full[is], (n_item / kT2Items) & 1, abort_flag)) break;
+      const int seq = s_item[is].seq, h = s_item[is].h, q_row = s_item[is].q_row, tq0 = s_item[is].tq0, Lq = s_item[is].Lq;
+      const int nA = s_item[is].n[0], nB = s_item[is].n[1];
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bar_item_empty[is]);
+      if (seq < 0) break;
+      ++n_item;
+#pragma unroll 1
+      for (int hx = 0; hx < 2; ++hx) {
+        if ((hx == 0 ? nA : nB) <= 0) continue;
+        const uint32_t ph = nf[hx] & 1;
+        if (!mbar_wait(&bar_l_full[hx], ph, abort_flag)) { ok = false; break; }
+        const float inv = s_inv[hx][r];
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bar_l_empty[hx]);
+        if (!mbar_wait(&bar_o_final[hx], ph, abort_flag)) { ok = false; break; }
+        tc::fence_after_sync();
+        t2_output(p, tmem + 256 + hx * 128 + lane_base, &bar_o_free[hx], sStage + quarter * 2048, lane, quarter, hx,
+                  inv, q_row, h, tq0, Lq);
+        ++nf[hx];
+      }
+    }
   }
 
 #ifdef B200_TRACE
