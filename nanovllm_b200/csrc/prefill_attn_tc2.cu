@@ -317,26 +317,25 @@ prefill_attn_tc2_kernel(const PrefillParams p, const __grid_constant__ CUtensorM
         if (nB <= 1) tc::commit(&bar_q_empty[1]);
         for (int j = 0; j < n && ok; ++j) {
           const int vslot = vt % kT2Ring;
-          const uint32_t vph = (vt / kT2Ring) & 1;
-          bool k_next_waited = false;
+          // V_j and the next K tile land long before the softmax is through: their barriers are tested
+          // first, so that nothing but the issue itself stands between a half's P and its MMAs
+          if (!mbar_wait(&bar_v_full[vslot], (vt / kT2Ring) & 1, abort_flag)) { ok = false; break; }
+          if (j + 1 < n && !mbar_wait(&bar_k_full[kt % kT2Ring], (kt / kT2Ring) & 1, abort_flag)) { ok = false; break; }
+          if (j == 0) {
+            if (nA > 0 && !mbar_wait(&bar_o_free[0], (no[0] & 1) ^ 1, abort_flag)) { ok = false; break; }
+            if (nB > 0 && !mbar_wait(&bar_o_free[1], (no[1] & 1) ^ 1, abort_flag)) { ok = false; break; }
+          }
           for (int hx = 0; hx < 2 && ok; ++hx) {
             const int nx = hx == 0 ? nA : nB;
             if (j >= nx) continue;
             // O_X += P_X V_j
             if (!mbar_wait(&bar_p_full[hx], np[hx] & 1, abort_flag)) { ok = false; break; }
             ++np[hx];
-            if (j == 0 && !mbar_wait(&bar_o_free[hx], (no[hx] & 1) ^ 1, abort_flag)) { ok = false; break; }
-            if (!mbar_wait(&bar_v_full[vslot], vph, abort_flag)) { ok = false; break; }
             tc::fence_after_sync();
             issue_pv(hx, vslot, j > 0);
             if (j == nx - 1) { tc::commit(&bar_o_final[hx]); ++no[hx]; }
             // S_X for the next K tile (its buffer is free: the PV above reads P before it runs)
             if (j + 1 < nx) {
-              if (!k_next_waited) {
-                if (!mbar_wait(&bar_k_full[kt % kT2Ring], (kt / kT2Ring) & 1, abort_flag)) { ok = false; break; }
-                tc::fence_after_sync();
-                k_next_waited = true;
-              }
               issue_s(hx, kt % kT2Ring);
               if (j + 2 >= nx) tc::commit(&bar_q_empty[hx]);   // that was the half's last S: its Q tile is free
             }
