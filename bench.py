@@ -51,8 +51,9 @@ def peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
         p = json.load(open(path))
-        return dict(hbm=float(p["hbm_gbs"]), bf16=float(p["bf16_tflops"]), source="measured")
-    return dict(hbm=6650.0, bf16=1590.0, source="fallback")
+        return dict(hbm=float(p["hbm_gbs"]), bf16=float(p["bf16_tflops"]),
+                    bf16_sustained=float(p.get("bf16_tflops_sustained", p["bf16_tflops"])), source="measured")
+    return dict(hbm=6650.0, bf16=1590.0, bf16_sustained=1400.0, source="fallback")
 
 
 class ClockSampler:
@@ -395,10 +396,14 @@ def secondary_prefill(dev, iters=10, workload="prefill_cfg3"):
     ms = a.elapsed_time(b) / iters
     pk = peaks()
     tf = flops / (ms * 1e-3) / 1e12
+    # a timed region of a few launches runs at burst clocks; a long one settles under the power cap,
+    # where the cuBLAS figure to compare with is the sustained one
+    kind = "sustained" if ms * iters > 250.0 else "burst"
+    peak = pk["bf16_sustained"] if kind == "sustained" else pk["bf16"]
     return {"metric": "prefill_attn_tflops", "workload": label,
             "value": round(tf, 1), "unit": "TFLOP/s", "ms": round(ms, 4), "flops": flops,
-            "frac_of_bf16_peak": round(tf / pk["bf16"], 4), "peak": pk["bf16"], "peak_source": pk["source"],
-            "frac_of_spec_2250": round(tf / 2250.0, 4)}
+            "frac_of_bf16_peak": round(tf / peak, 4), "peak": peak, "peak_source": pk["source"], "peak_kind": kind,
+            "timed_ms": round(ms * iters, 1), "frac_of_spec_2250": round(tf / 2250.0, 4)}
 
 
 def run_prefill(args, w, rank, world, local):
@@ -411,7 +416,8 @@ def run_prefill(args, w, rank, world, local):
             "warmup": 3, "ms_per_step": s["ms"], "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic", "config": {"workload": s["workload"]},
             "roofline": {"bound": "tensor", "achieved": s["value"], "peak": s["peak"], "unit": "TFLOP/s",
-                         "frac": s["frac_of_bf16_peak"], "peak_source": s["peak_source"], "traffic": None}}
+                         "frac": s["frac_of_bf16_peak"], "peak_source": s["peak_source"], "peak_kind": s["peak_kind"],
+                         "timed_ms": s["timed_ms"], "traffic": None}}
 
 
 def main():
