@@ -41,6 +41,8 @@ int sm_count();                                  // multiprocessors of the curre
 // q/k/v activations with arbitrary row stride.
 int make_tokens_heads_map(CUtensorMap* map, const void* base, uint64_t tokens, uint32_t heads,
                           uint64_t row_stride_elems, uint32_t box_tokens, uint32_t box_heads = 1);
+int make_tokens_heads_map_cols32(CUtensorMap* map, const void* base, uint64_t tokens, uint32_t heads,
+                                 uint64_t row_stride_elems, uint32_t box_tokens, uint32_t box_heads);
 
 #ifdef __CUDACC__
 
@@ -107,6 +109,21 @@ __device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, u
       " [%0], [%1, {%3, %4, %5}], [%2];"
       ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
       : "memory");
+}
+// TMA tile store, 3-D, from this CTA's shared memory (bulk-group completion).
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, const void* src, int c0, int c1, int c2) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4}], [%1];"
+               ::"l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(src)), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// Returns once the bulk stores of this thread have finished READING their shared-memory source.
+__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// The same, but the most recent store may still be reading.
+__device__ __forceinline__ void tma_store_wait_read_but_one() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
+// Hint: bring one box of a 3-D tensor map into L2 (no shared-memory destination, no completion to wait for).
+__device__ __forceinline__ void tma_prefetch_l2_3d(const CUtensorMap* map, int c0, int c1, int c2) {
+  asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];"
+               ::"l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(c2) : "memory");
 }
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");

@@ -73,6 +73,26 @@ int make_tokens_heads_map(CUtensorMap* map, const void* base, uint64_t tokens, u
   return kOk;
 }
 
+// Output form of the same map: boxes of {32 dims, box_heads, box_tokens} with a 64-byte swizzle
+// (a box row is 64 bytes; 16-byte chunk c of row r sits at chunk c ^ ((r >> 1) & 3)).
+int make_tokens_heads_map_cols32(CUtensorMap* map, const void* base, uint64_t tokens, uint32_t heads,
+                                 uint64_t row_stride_elems, uint32_t box_tokens, uint32_t box_heads) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return set_error(kErrNoDriver, "cuTensorMapEncodeTiled is not available (no CUDA driver?)");
+  if (tokens == 0) tokens = 1;
+  cuuint64_t dims[3] = {128, heads, tokens};
+  cuuint64_t strides[2] = {128 * 2, row_stride_elems * 2};
+  cuuint32_t box[3] = {32, box_heads, box_tokens};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return set_error(kErrTensorMap, "cuTensorMapEncodeTiled (output map) failed with CUresult %d (tokens=%llu heads=%u)",
+                     static_cast<int>(r), (unsigned long long)tokens, heads);
+  return kOk;
+}
+
 }  // namespace b200
 
 extern "C" {

@@ -20,6 +20,7 @@ struct PrefillParams {
   int n_slots;  // upper bound on query tiles: total_q / QT + batch
   int total_q, max_seqlen_q, max_seqlen_k;
   float scale_log2;
+  int out_tma;  // tc2: the output map (boxes of 32 tile rows) is usable: 32 % G == 0
 };
 
 // mma.sync variant: K/V maps with 64-token boxes.
@@ -31,7 +32,7 @@ int launch_prefill_tc(const PrefillParams& p, const CUtensorMap& map_q, const CU
 
 // tcgen05 variant, persistent with two query tiles per CTA sharing each K/V tile (same maps as above).
 int launch_prefill_tc2(PrefillParams p, const CUtensorMap& map_q, const CUtensorMap& map_k, const CUtensorMap& map_v,
-                       cudaStream_t stream);
+                       const CUtensorMap& map_o, cudaStream_t stream);
 
 // tcgen05 variant, persistent, 64-key steps with double-buffered S (K/V maps with 64-token boxes).
 int launch_prefill_tc3(PrefillParams p, const CUtensorMap& map_q, const CUtensorMap& map_k, const CUtensorMap& map_v,

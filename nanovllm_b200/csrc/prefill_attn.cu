@@ -87,6 +87,7 @@ extern "C" int b200_prefill_attn(const void* q, int64_t q_row_stride, const void
   p.total_q = total_q;
   p.max_seqlen_q = max_seqlen_q;
   p.max_seqlen_k = max_seqlen_k;
+  p.out_tma = 0;
   if (use_tc) {
     CUtensorMap map_q;
     rc = make_tokens_heads_map(&map_q, q, static_cast<uint64_t>(total_q), num_heads, static_cast<uint64_t>(q_row_stride),
@@ -94,7 +95,16 @@ extern "C" int b200_prefill_attn(const void* q, int64_t q_row_stride, const void
     if (rc) return rc;
     if (kernel_variant == 2) return launch_prefill_tc(p, map_q, map_k, map_v, static_cast<cudaStream_t>(stream));
     if (kernel_variant == 4) return launch_prefill_tc3(p, map_q, map_k, map_v, static_cast<cudaStream_t>(stream));
-    return launch_prefill_tc2(p, map_q, map_k, map_v, static_cast<cudaStream_t>(stream));
+    // output map of the persistent kernel: boxes of 32 tile rows = (32 / G tokens) x (G heads) x 32 dims
+    CUtensorMap map_o = map_q;
+    p.out_tma = 32 % G == 0;
+    if (p.out_tma) {
+      rc = make_tokens_heads_map_cols32(&map_o, out, static_cast<uint64_t>(total_q), num_heads,
+                                        static_cast<uint64_t>(num_heads) * 128, static_cast<uint32_t>(32 / G),
+                                        static_cast<uint32_t>(G));
+      if (rc) return rc;
+    }
+    return launch_prefill_tc2(p, map_q, map_k, map_v, map_o, static_cast<cudaStream_t>(stream));
   }
   return launch_prefill_mma(p, map_k, map_v, static_cast<cudaStream_t>(stream));
 }

@@ -14,8 +14,11 @@
 //   warps 4-7     softmax warpgroup of half A: thread r owns TMEM lane r = one query row; reads S
 //                 with tcgen05.ld, keeps max / sum in registers, writes P (bf16) over S with
 //                 tcgen05.st, rescales O in TMEM only when the row max grew by more than 2^8;
-//   warps 8-11    the same for half B.  (Warps 2-3 idle; setmaxnreg moves their registers and
-//                 most of the producer's and issuer's to the softmax warpgroups.)
+//   warps 8-11    the same for half B;
+//   warps 12-15   output warpgroup: takes a finished O out of TMEM, scales it by 1 / row sum and
+//                 sends it out as bf16 through TMA stores (plain stores where a box would overhang
+//                 the sequence), so the softmax warpgroups never stop for output.
+//   (Warps 2-3 idle; setmaxnreg: warpgroup 0 -> 72, softmax -> 184, output -> 72 registers.)
 // TMEM: S_A [0,128)  S_B [128,256)  O_A [256,384)  O_B [384,512).  Every mbarrier wait is bounded.
 #include <atomic>
 
@@ -109,9 +112,58 @@ __device__ __forceinline__ void t2_output(const PrefillParams& p, uint32_t tmem_
   }
 }
 
+// The same for a warp whose 32 tile rows are all real query rows: the scaled bf16 rows are laid out
+// in shared memory as two 128-byte-swizzled boxes of 64 dims and leave through two TMA stores, so
+// the warp issues no global store and no read-back at all.  `stage` is 4 KiB, 1024-byte aligned.
+__device__ __forceinline__ void t2_stage_chunk(const uint32_t (&ov)[16], unsigned char* box, int lane, int c, float inv) {
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    uint4 w;
+    w.x = pack_bf16(__uint_as_float(ov[8 * i]) * inv, __uint_as_float(ov[8 * i + 1]) * inv);
+    w.y = pack_bf16(__uint_as_float(ov[8 * i + 2]) * inv, __uint_as_float(ov[8 * i + 3]) * inv);
+    w.z = pack_bf16(__uint_as_float(ov[8 * i + 4]) * inv, __uint_as_float(ov[8 * i + 5]) * inv);
+    w.w = pack_bf16(__uint_as_float(ov[8 * i + 6]) * inv, __uint_as_float(ov[8 * i + 7]) * inv);
+    *reinterpret_cast<uint4*>(box + lane * 64 + (((2 * c + i) ^ ((lane >> 1) & 3)) << 4)) = w;   // 64-byte swizzle
+  }
+}
+// `stage` holds two boxes of 32 rows x 32 dims (2 KiB each, 64-byte swizzle) used in turn, so that
+// a box is written while the TMA engine still reads the one before.
+__device__ __forceinline__ void t2_output_tma(const CUtensorMap* map_o, uint32_t tmem_o_lane, uint64_t* bar_o_free,
+                                              unsigned char* stage, int lane, float inv, int head0, int tok0) {
+  // eight 16-column chunks, the TMEM load of the next one in flight while one is converted
+  uint32_t a[16], b[16];
+  tc::ld_32x32b_x16(tmem_o_lane, a);
+#pragma unroll
+  for (int bx = 0; bx < 4; ++bx) {
+    unsigned char* box = stage + (bx & 1) * 2048;
+    if (lane == 0) tma_store_wait_read_but_one();        // the store before the previous one has left this box
+    __syncwarp();
+    tc::wait_ld();
+    tc::ld_32x32b_x16(tmem_o_lane + bx * 32 + 16, b);
+    t2_stage_chunk(a, box, lane, 0, inv);
+    tc::wait_ld();
+    if (bx == 3) {
+      // the accumulator is in registers: the issuer may start the next item's PV
+      tc::fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_o_free);
+    } else {
+      tc::ld_32x32b_x16(tmem_o_lane + bx * 32 + 32, a);
+    }
+    t2_stage_chunk(b, box, lane, 1, inv);
+    fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0) {
+      tma_store_3d(map_o, box, bx * 32, head0, tok0);
+      tma_store_commit();
+    }
+  }
+}
+
 __global__ void __launch_bounds__(kT2Threads, 1)
 prefill_attn_tc2_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap map_q,
-                        const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v) {
+                        const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                        const __grid_constant__ CUtensorMap map_o) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   unsigned char* sQ = smem;                              // [2][32 KiB]
@@ -169,7 +221,7 @@ prefill_attn_tc2_kernel(const PrefillParams p, const __grid_constant__ CUtensorM
   // Registers move from the light warpgroup to the two softmax warpgroups, which hold a whole
   // 128-column S row (and later the O row) per thread.
   if (warp < 4) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 80;" ::: "memory");
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 72;" ::: "memory");
   if (warp == 0) {
     // ================================ TMA producer ================================
     if (lane == 0) {
@@ -225,6 +277,14 @@ prefill_attn_tc2_kernel(const PrefillParams p, const __grid_constant__ CUtensorM
         s_item[is].seq = seq;
         mbar_arrive(&bar_item_full[is]);                                // an item, or the end marker
         if (seq < 0) break;
+        // The Q tiles can only be loaded once the previous item has let go of the buffers, which is when
+        // they are needed: start them on their way into L2 now, with the item's first K/V tile.
+        tma_prefetch_l2_3d(&map_q, 0, h * G, q_row);
+        tma_prefetch_l2_3d(&map_q, 64, h * G, q_row);
+        if (b_rows) {
+          tma_prefetch_l2_3d(&map_q, 0, h * G, q_row + QT);
+          tma_prefetch_l2_3d(&map_q, 64, h * G, q_row + QT);
+        }
         PF_TRACE(n_pub, 0);
         // Q tiles (the buffers are free once every S MMA of the previous item has completed)
         const uint32_t qph = (n_pub & 1) ^ 1;
@@ -293,6 +353,9 @@ prefill_attn_tc2_kernel(const PrefillParams p, const __grid_constant__ CUtensorM
           tc::mma_ts_lo(tmem + 256 + hx * 128, tmem + hx * 128 + ks * 8, v_lo + vslot * (kT2Tile >> 4) + ks * (2048 >> 4),
                         desc_hi, idesc_pv, accumulate || ks > 0);
       };
+#ifdef B200_TRACE
+      long long mk_of = 0;
+#endif
       while (ok) {
         const int is = n_item % kT2Items;
         if (!mbar_wait(&bar_item_full[is], (n_item / kT2Items) & 1, abort_flag)) break;
@@ -318,12 +381,19 @@ prefill_attn_tc2_kernel(const PrefillParams p, const __grid_constant__ CUtensorM
         for (int j = 0; j < n && ok; ++j) {
           const int vslot = vt % kT2Ring;
           // V_j and the next K tile land long before the softmax is through: their barriers are tested
-          // first, so that nothing but the issue itself stands between a half's P and its MMAs
+          // first, so that little but the issue itself stands between a half's P and its MMAs
           if (!mbar_wait(&bar_v_full[vslot], (vt / kT2Ring) & 1, abort_flag)) { ok = false; break; }
           if (j + 1 < n && !mbar_wait(&bar_k_full[kt % kT2Ring], (kt / kT2Ring) & 1, abort_flag)) { ok = false; break; }
           if (j == 0) {
+            // the output warpgroup must have taken the previous item's O out of both accumulators
+#ifdef B200_TRACE
+            const long long tof = clock64();
+#endif
             if (nA > 0 && !mbar_wait(&bar_o_free[0], (no[0] & 1) ^ 1, abort_flag)) { ok = false; break; }
             if (nB > 0 && !mbar_wait(&bar_o_free[1], (no[1] & 1) ^ 1, abort_flag)) { ok = false; break; }
+#ifdef B200_TRACE
+            mk_of += clock64() - tof;
+#endif
           }
           for (int hx = 0; hx < 2 && ok; ++hx) {
             const int nx = hx == 0 ? nA : nB;
@@ -348,10 +418,16 @@ prefill_attn_tc2_kernel(const PrefillParams p, const __grid_constant__ CUtensorM
         PF_TRACE(n_item, 5);
         ++n_item;
       }
+#ifdef B200_TRACE
+      if (blockIdx.x < 8) {
+        unsigned long long* o = g_pf_trace + (blockIdx.x * kT2TraceItems + (kT2TraceItems - 2)) * kT2TraceSlots;
+        o[0] = n_item; o[1] = mk_of;
+      }
+#endif
     }
   }
   } else if (warp < 12) {
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 192;" ::: "memory");
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 184;" ::: "memory");
     // ================================ softmax / epilogue ================================
     const int hx = (warp - 4) >> 2;                     // which half this warpgroup serves
     const int quarter = warp & 3;                       // TMEM lanes this warp may touch
@@ -532,7 +608,7 @@ prefill_attn_tc2_kernel(const PrefillParams p, const __grid_constant__ CUtensorM
     }
 #endif
   } else {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 48;" ::: "memory");
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 72;" ::: "memory");
     // ================================ output warpgroup ================================
     const int quarter = warp & 3;
     const int r = quarter * 32 + lane;
@@ -540,9 +616,16 @@ prefill_attn_tc2_kernel(const PrefillParams p, const __grid_constant__ CUtensorM
     int n_item = 0;
     int nf[2] = {0, 0};                                  // halves drained so far
     bool ok = true;
+#ifdef B200_TRACE
+    long long ok_item = 0, ok_l = 0, ok_of = 0, ok_drain = 0, ok_n = 0, ok_t0 = clock64();
+#define OK(var) do { const long long now_ = clock64(); var += now_ - ok_t0; ok_t0 = now_; } while (0)
+#else
+#define OK(var) do { } while (0)
+#endif
     while (ok) {
       const int is = n_item % kT2Items;
       if (!mbar_wait(&bar_item_full[is], (n_item / kT2Items) & 1, abort_flag)) break;
+      OK(ok_item);
       const int seq = s_item[is].seq, h = s_item[is].h, q_row = s_item[is].q_row, tq0 = s_item[is].tq0, Lq = s_item[is].Lq;
       const int nA = s_item[is].n[0], nB = s_item[is].n[1];
       __syncwarp();
@@ -554,16 +637,37 @@ prefill_attn_tc2_kernel(const PrefillParams p, const __grid_constant__ CUtensorM
         if ((hx == 0 ? nA : nB) <= 0) continue;
         const uint32_t ph = nf[hx] & 1;
         if (!mbar_wait(&bar_l_full[hx], ph, abort_flag)) { ok = false; break; }
+        OK(ok_l);
         const float inv = s_inv[hx][r];
         __syncwarp();
         if (lane == 0) mbar_arrive(&bar_l_empty[hx]);
         if (!mbar_wait(&bar_o_final[hx], ph, abort_flag)) { ok = false; break; }
+        OK(ok_of);
         tc::fence_after_sync();
-        t2_output(p, tmem + 256 + hx * 128 + lane_base, &bar_o_free[hx], sStage + quarter * 2048, lane, quarter, hx,
-                  inv, q_row, h, tq0, Lq);
+        const int tok_w = tq0 + hx * QT + (quarter * 32) / G;        // first token of this warp's rows
+        if (p.out_tma && tok_w + 32 / G <= Lq) {
+          t2_output_tma(&map_o, tmem + 256 + hx * 128 + lane_base, &bar_o_free[hx], sStage + quarter * 4096, lane, inv,
+                        h * G, q_row + hx * QT + (quarter * 32) / G);
+        } else {
+          if (lane == 0) tma_store_wait_read();
+          __syncwarp();
+          t2_output(p, tmem + 256 + hx * 128 + lane_base, &bar_o_free[hx], sStage + quarter * 4096, lane, quarter, hx,
+                    inv, q_row, h, tq0, Lq);
+        }
+        OK(ok_drain);
+#ifdef B200_TRACE
+        ++ok_n;
+#endif
         ++nf[hx];
       }
     }
+    if (lane == 0) tma_store_wait_read();                // the staging tile must outlive its last store
+#ifdef B200_TRACE
+    if (warp == 12 && lane == 0 && blockIdx.x < 8) {
+      unsigned long long* o = g_pf_trace + (blockIdx.x * kT2TraceItems + (kT2TraceItems - 3)) * kT2TraceSlots;
+      o[0] = ok_n; o[1] = ok_item; o[2] = ok_l; o[3] = ok_of; o[4] = ok_drain;
+    }
+#endif
   }
 
 #ifdef B200_TRACE
@@ -595,7 +699,7 @@ int read_status_prefill_tc2() {
 
 // Needs whole query heads groups in a 128-row tile.  The query-block slots are laid out for 2 * QT tokens.
 int launch_prefill_tc2(PrefillParams p, const CUtensorMap& map_q, const CUtensorMap& map_k, const CUtensorMap& map_v,
-                       cudaStream_t stream) {
+                       const CUtensorMap& map_o, cudaStream_t stream) {
   p.n_slots = p.total_q / (2 * p.QT) + p.batch;
   const size_t smem = 1024 + static_cast<size_t>(2 + 2 * kT2Ring) * kT2Tile + 8 * 2048 +
                       (p.batch <= kT2MaxSeqSmem ? (p.batch + 1) * 4 : 4) + 64;
@@ -609,7 +713,7 @@ int launch_prefill_tc2(PrefillParams p, const CUtensorMap& map_q, const CUtensor
   const int grid = sm_count();
   if (grid <= 0) return set_error(kErrNoDriver, "prefill_attn: no CUDA device");
   if (static_cast<long long>(p.n_slots) * p.Hkv > 0x7fffffffLL) return set_error(kErrBadShape, "prefill_attn: too many query blocks");
-  prefill_attn_tc2_kernel<<<grid, kT2Threads, smem, stream>>>(p, map_q, map_k, map_v);
+  prefill_attn_tc2_kernel<<<grid, kT2Threads, smem, stream>>>(p, map_q, map_k, map_v, map_o);
   g_launches.fetch_add(1);
   return check_cuda(cudaGetLastError(), "prefill_attn(tc2) launch");
 }
