@@ -343,7 +343,7 @@ def _variants(h, hkv):
 
 
 @pytest.mark.parametrize("variant", ["mma", "tcgen05", "tcgen05_persistent", "tcgen05_persistent_kv64"])
-@pytest.mark.parametrize("h,hkv", [(16, 8), (4, 1), (2, 2), (5, 1), (8, 1)])
+@pytest.mark.parametrize("h,hkv", [(16, 8), (4, 1), (2, 2), (5, 1), (8, 1), (32, 1), (64, 1)])
 def test_prefill_dense_ragged(b200, h, hkv, variant):
     pkg, _ = b200
     if variant not in _variants(h, hkv):
