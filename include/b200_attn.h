@@ -121,9 +121,11 @@ int b200_decode_attn_static(const void* q, int64_t q_row_stride, const void* k_c
  * max_seqlen_q / max_seqlen_k are the host-side bounds the caller already has
  * (nanovllm/utils/context.py:9-10).  kernel_variant: 0 = default (the persistent tcgen05 kernel
  * when 128 % (num_heads / num_kv_heads) == 0, else the mma.sync kernel), 1 = force the mma.sync
- * kernel, 2 = force the one-tile-per-CTA tcgen05 kernel, 3 = force the persistent tcgen05 kernel
- * (2 and 3 return B200_ERR_BAD_SHAPE if they cannot take the shape).  Launches of the persistent
- * kernel share one device-side ticket counter: do not overlap two of them on one GPU. */
+ * kernel, 2 = force the one-tile-per-CTA tcgen05 kernel, 3 = force the persistent tcgen05 kernel,
+ * 4 = force the experimental persistent tcgen05 kernel with 64-key steps (2, 3 and 4 return
+ * B200_ERR_BAD_SHAPE if they cannot take the shape).  Launches of the persistent kernels share
+ * one device-side ticket counter: do not overlap two of them on one GPU.  The persistent kernel
+ * writes `out` through TMA stores: out must be 16-byte aligned (as every tensor here). */
 int b200_prefill_attn(const void* q, int64_t q_row_stride, const void* k, const void* v, int64_t k_row_stride,
                       int64_t v_row_stride, int64_t total_k, const void* k_cache, const void* v_cache,
                       int64_t num_blocks, int32_t block_size, const int32_t* block_tables, int64_t bt_row_stride,
