@@ -2,7 +2,7 @@
 """End-to-end output tokens/s of the nano-vllm engine with either attention layer
 (BASELINE config 5: the workload of the reference's own bench.py).
 
-    python bench_e2e.py --attn ours|reference [--tp 1] [--num-seqs 256] [--out FILE]
+    python bench_e2e.py --attn ours|reference [--fuse-producer] [--tp 1] [--num-seqs 256] [--out FILE]
 
 The ENGINE is the unmodified reference (scheduler, block manager, model runner, Qwen3 model,
 CUDA graphs, sampler) imported from --ref (default baseline/_ref, a pip --target install of the
@@ -41,7 +41,7 @@ for _p in (ROOT, _REF):
 # model runner, so the layer is installed here, at import time, in every process of the `ours` arm.
 if os.environ.get("B200_E2E_ATTN") == "ours":
     import nanovllm_b200.integration as _integ
-    _integ.install()
+    _integ.install(fuse_qk_norm_rope=os.environ.get("B200_E2E_FUSE") == "1")
 
 
 def make_model_dir(path: str):
@@ -107,10 +107,14 @@ def main():
     ap.add_argument("--num-seqs", type=int, default=256)
     ap.add_argument("--model-dir", default="/tmp/b200_e2e_qwen3_0p6b_random")
     ap.add_argument("--out", default="")
+    ap.add_argument("--fuse-producer", action="store_true",
+                    help="with --attn ours: q_norm + k_norm + rotary_emb + cache store as one kernel")
     args = ap.parse_args()
-    if os.environ.get("B200_E2E_ATTN") != args.attn:
+    want_fuse = "1" if (args.fuse_producer and args.attn == "ours") else "0"
+    if os.environ.get("B200_E2E_ATTN") != args.attn or os.environ.get("B200_E2E_FUSE", "0") != want_fuse:
         # set before anything of the engine is imported (and for spawned ranks), then start over
         os.environ["B200_E2E_ATTN"] = args.attn
+        os.environ["B200_E2E_FUSE"] = want_fuse
         os.execv(sys.executable, [sys.executable] + sys.argv)
 
     import torch
@@ -140,6 +144,7 @@ def main():
     produced = sum(len(o["token_ids"]) for o in outs)
     res = {
         "metric": "e2e_output_tok_per_s", "value": round(total / t, 2), "unit": "tok/s", "attn": args.attn,
+        "fused_producer": want_fuse == "1",
         "attention_module": attn_mod.__name__ + " from " + os.path.relpath(attn_mod.__file__, ROOT),
         "tp": args.tp, "num_seqs": args.num_seqs, "output_tokens": total, "produced_tokens": produced,
         "input_tokens": sum(len(p) for p in prompts), "seconds": round(t, 3), "engine_init_s": round(t_init, 1),

@@ -133,6 +133,26 @@ int b200_prefill_attn(const void* q, int64_t q_row_stride, const void* k, const 
                       int32_t total_q, int32_t max_seqlen_q, int32_t max_seqlen_k, void* out, int32_t num_heads,
                       int32_t num_kv_heads, int32_t head_dim, float scale, int32_t kernel_variant, void* stream);
 
+/* ---- producer side of the layer: QK-norm + rotary embedding + cache store in one launch -------------------
+ * Replaces, for one decoder layer and one step, what the reference runs between its fused qkv projection
+ * and its attention call (nanovllm/models/qwen3.py:75-79 and nanovllm/layers/attention.py:62-63):
+ *   q_norm, k_norm   nanovllm/layers/layernorm.py:16-26       fp32 RMS normalisation over head_dim, cast to
+ *                                                              bf16, times the bf16 weight
+ *   rotary_emb       nanovllm/layers/rotary_embedding.py:6-14  rotate-half with cos/sin gathered by position
+ *   store_kvcache    nanovllm/layers/attention.py:10-40        k (after norm and rotation) and v to their slots
+ * qkv is the (n_tokens, (num_heads + 2 * num_kv_heads) * 128) bf16 output of the fused projection with row
+ * stride qkv_row_stride (elements); positions are int64 as in the reference; cos_sin_cache is the reference's
+ * (max_position, 1, 128) fp32 table (64 cos then 64 sin per position).  q_out (n_tokens, num_heads, 128) and
+ * k_out (n_tokens, num_kv_heads, 128) are written contiguous (dense prefill reads k from there).  With
+ * k_cache / v_cache given, token i's k and v rows also go to flat cache row slot_mapping[i] (-1 and slots
+ * >= n_slots are skipped); both NULL = no store (the engine's warm-up pass).  v is never copied anywhere else:
+ * the attention call keeps reading it as a view of qkv. */
+int b200_qk_norm_rope_store(const void* qkv, int64_t qkv_row_stride, const int64_t* positions, const void* q_weight,
+                            const void* k_weight, const float* cos_sin_cache, int32_t max_position, float eps,
+                            void* q_out, void* k_out, void* k_cache, void* v_cache, const int32_t* slot_mapping,
+                            int64_t n_slots, int32_t n_tokens, int32_t num_heads, int32_t num_kv_heads,
+                            int32_t head_dim, void* stream);
+
 /* Number of kernels this library has launched from the calling process so far (all threads).
  * Benchmarks use the difference across a timed region. */
 int64_t b200_launch_count(void);

@@ -31,6 +31,9 @@ SIGNATURES = {
                                     c_void_p, c_int64, c_int32, c_void_p, c_int64, c_int32, c_void_p, c_void_p,
                                     c_int32, c_int32, c_int32, c_int32, c_void_p, c_int32, c_int32, c_int32,
                                     c_float, c_int32, c_void_p]),
+    "b200_qk_norm_rope_store": (c_int32, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_float,
+                                          c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int32, c_int32,
+                                          c_int32, c_int32, c_void_p]),
     "b200_launch_count": (c_int64, []),
     "b200_device_status": (c_int32, []),
 }

@@ -19,7 +19,10 @@ import importlib
 import sys
 
 
-def install():
+def install(fuse_qk_norm_rope: bool = False):
+    """fuse_qk_norm_rope=True additionally replaces the body of `Qwen3Attention.forward`
+    (nanovllm/models/qwen3.py:68-82) by one that runs q_norm, k_norm, rotary_emb and the cache store as a
+    single kernel (layers/qk_norm_rope.py); nano-vllm's model module is imported for that."""
     from .layers import attention as ours
     ref_attn = sys.modules.get("nanovllm.layers.attention")
     if ref_attn is None:
@@ -37,4 +40,8 @@ def install():
     qwen3 = sys.modules.get("nanovllm.models.qwen3")
     if qwen3 is not None:
         qwen3.Attention = ours.Attention
+    if fuse_qk_norm_rope:
+        from .layers.qk_norm_rope import fused_attention_forward
+        qwen3 = importlib.import_module("nanovllm.models.qwen3")
+        qwen3.Qwen3Attention.forward = fused_attention_forward
     return ours
