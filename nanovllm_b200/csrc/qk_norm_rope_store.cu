@@ -5,8 +5,8 @@
 //   store_kvcache        nanovllm/layers/attention.py:10-40    (called at layers/attention.py:62-63)
 // which the reference runs as three compiled element-wise kernels plus one Triton kernel.
 //
-// One warp owns one 128-element head vector of one token: lane l holds elements [4l, 4l + 4), so the
-// rotary partner (element i +- 64) of every element sits in lane l ^ 16.  q heads and k heads are
+// A half-warp owns one 128-element head vector of one token: lane j of 16 holds elements [8j, 8j + 8)
+// (16-byte accesses), so the rotary partner (element i +- 64) of every element sits in lane j ^ 8.  q heads and k heads are
 // normalised in fp32, cast to bf16, multiplied by the bf16 weight, rotated in fp32 (products and
 // sums rounded separately, as the reference's eager arithmetic does) and written out contiguous;
 // k is also written to its cache slot.  v heads are copied bit-for-bit from the strided qkv row to
@@ -39,71 +39,98 @@ struct QkNormRopeParams {
   int n_tokens, H, Hkv;
 };
 
-constexpr int kQkWarps = 8;
+constexpr int kQkThreads = 256;     // 16 head vectors per CTA pass: one per half-warp
 
-__global__ void __launch_bounds__(kQkWarps * 32)
+__device__ __forceinline__ void bf16x8_to_float(const uint4& r, float (&x)[8]) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&r);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    x[2 * i] = __low2float(h[i]);
+    x[2 * i + 1] = __high2float(h[i]);
+  }
+}
+
+// One head vector: `raw` holds this lane's 8 elements of head `hd` of token `tok`.
+__device__ __forceinline__ void qk_one_vector(const QkNormRopeParams& p, int tok, int hd, const uint4& raw, int sub,
+                                              unsigned half_mask) {
+  long long slot = -1;
+  if (p.slot_mapping && p.k_cache && p.v_cache) {
+    slot = p.slot_mapping[tok];
+    if (slot >= p.n_slots) slot = -1;                    // never write outside the cache
+  }
+  if (hd >= p.H + p.Hkv) {
+    // v head: a bit copy into the cache
+    if (slot >= 0)
+      *reinterpret_cast<uint4*>(p.v_cache + (slot * p.Hkv + (hd - p.H - p.Hkv)) * 128 + sub * 8) = raw;
+    return;
+  }
+  const bool is_q = hd < p.H;
+  long long pos = p.positions[tok];
+  pos = pos < 0 ? 0 : (pos >= p.max_position ? p.max_position - 1 : pos);
+  const float* cs = p.cos_sin + pos * 128 + (sub & 7) * 8;
+  const float4 c0 = *reinterpret_cast<const float4*>(cs), c1 = *reinterpret_cast<const float4*>(cs + 4);
+  const float4 s0 = *reinterpret_cast<const float4*>(cs + 64), s1 = *reinterpret_cast<const float4*>(cs + 68);
+  const uint4 wraw = *reinterpret_cast<const uint4*>((is_q ? p.q_weight : p.k_weight) + sub * 8);
+  float x[8], w[8];
+  bf16x8_to_float(raw, x);
+  bf16x8_to_float(wraw, w);
+  // mean of squares over the 128 elements, fp32
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) ss = __fadd_rn(ss, __fmul_rn(x[i], x[i]));
+#pragma unroll
+  for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(half_mask, ss, o);
+  const float rinv = __frsqrt_rn(__fadd_rn(__fdiv_rn(ss, 128.f), p.eps));
+  const float cosv[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+  const float sinv[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+  float y[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    // normalise in fp32, round to bf16, scale by the bf16 weight (rounded to bf16 again)
+    const float xn = __bfloat162float(__float2bfloat16_rn(__fmul_rn(x[i], rinv)));
+    const float a = __bfloat162float(__float2bfloat16_rn(__fmul_rn(xn, w[i])));
+    const float b = __shfl_xor_sync(half_mask, a, 8);             // the element 64 away
+    // first half:  y1 = x1 * cos - x2 * sin      second half:  y2 = x2 * cos + x1 * sin
+    y[i] = sub < 8 ? __fsub_rn(__fmul_rn(a, cosv[i]), __fmul_rn(b, sinv[i]))
+                   : __fadd_rn(__fmul_rn(a, cosv[i]), __fmul_rn(b, sinv[i]));
+  }
+  uint4 outw;
+  outw.x = pack_bf16(y[0], y[1]);
+  outw.y = pack_bf16(y[2], y[3]);
+  outw.z = pack_bf16(y[4], y[5]);
+  outw.w = pack_bf16(y[6], y[7]);
+  if (is_q) {
+    *reinterpret_cast<uint4*>(p.q_out + (static_cast<long long>(tok) * p.H + hd) * 128 + sub * 8) = outw;
+  } else {
+    const int kh = hd - p.H;
+    *reinterpret_cast<uint4*>(p.k_out + (static_cast<long long>(tok) * p.Hkv + kh) * 128 + sub * 8) = outw;
+    if (slot >= 0) *reinterpret_cast<uint4*>(p.k_cache + (slot * p.Hkv + kh) * 128 + sub * 8) = outw;
+  }
+}
+
+__global__ void __launch_bounds__(kQkThreads)
 qk_norm_rope_store_kernel(const QkNormRopeParams p) {
-  const int lane = threadIdx.x & 31;
+  // a half-warp owns one head vector: lane j of 16 holds elements [8j, 8j + 8) (one 16-byte access),
+  // the rotary partner (element i +- 64) of each of them sits in lane j ^ 8; two vectors are in flight
+  // per half-warp so that the second load is on its way while the first is worked on
+  const int sub = threadIdx.x & 15;
   const int heads = p.H + 2 * p.Hkv;
   const long long n_vec = static_cast<long long>(p.n_tokens) * heads;
-  const long long stride = static_cast<long long>(gridDim.x) * kQkWarps;
+  const long long stride = static_cast<long long>(gridDim.x) * (kQkThreads / 16);
+  const unsigned half_mask = 0xffffu << (threadIdx.x & 16);
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  for (long long vec = static_cast<long long>(blockIdx.x) * kQkWarps + (threadIdx.x >> 5); vec < n_vec; vec += stride) {
+  for (long long vec = static_cast<long long>(blockIdx.x) * (kQkThreads / 16) + (threadIdx.x >> 4); vec < n_vec;
+       vec += 2 * stride) {
+    const long long vec2 = vec + stride;
     const int tok = static_cast<int>(vec / heads);
     const int hd = static_cast<int>(vec - static_cast<long long>(tok) * heads);
-    const uint2 raw = *reinterpret_cast<const uint2*>(p.qkv + tok * p.qkv_row_stride + hd * 128 + lane * 4);
-    long long slot = -1;
-    if (p.slot_mapping && p.k_cache && p.v_cache) {
-      slot = p.slot_mapping[tok];
-      if (slot >= p.n_slots) slot = -1;                    // never write outside the cache
-    }
-    if (hd >= p.H + p.Hkv) {
-      // v head: a bit copy into the cache
-      if (slot >= 0)
-        *reinterpret_cast<uint2*>(p.v_cache + (slot * p.Hkv + (hd - p.H - p.Hkv)) * 128 + lane * 4) = raw;
-      continue;
-    }
-    const bool is_q = hd < p.H;
-    const __nv_bfloat162 r01 = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
-    const __nv_bfloat162 r23 = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
-    float x[4] = {__low2float(r01), __high2float(r01), __low2float(r23), __high2float(r23)};
-    // mean of squares over the 128 elements, fp32
-    float ss = __fadd_rn(__fadd_rn(__fmul_rn(x[0], x[0]), __fmul_rn(x[1], x[1])),
-                         __fadd_rn(__fmul_rn(x[2], x[2]), __fmul_rn(x[3], x[3])));
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-    const float rinv = __frsqrt_rn(__fadd_rn(__fdiv_rn(ss, 128.f), p.eps));
-    const uint2 wraw = *reinterpret_cast<const uint2*>((is_q ? p.q_weight : p.k_weight) + lane * 4);
-    const __nv_bfloat162 w01 = *reinterpret_cast<const __nv_bfloat162*>(&wraw.x);
-    const __nv_bfloat162 w23 = *reinterpret_cast<const __nv_bfloat162*>(&wraw.y);
-    const float w[4] = {__low2float(w01), __high2float(w01), __low2float(w23), __high2float(w23)};
-    long long pos = p.positions[tok];
-    pos = pos < 0 ? 0 : (pos >= p.max_position ? p.max_position - 1 : pos);
-    const float* cs = p.cos_sin + pos * 128 + (lane & 15) * 4;
-    const float4 c4 = *reinterpret_cast<const float4*>(cs);
-    const float4 s4 = *reinterpret_cast<const float4*>(cs + 64);
-    const float cosv[4] = {c4.x, c4.y, c4.z, c4.w}, sinv[4] = {s4.x, s4.y, s4.z, s4.w};
-    float y[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      // normalise in fp32, round to bf16, scale by the bf16 weight (rounded to bf16 again)
-      const float xn = __bfloat162float(__float2bfloat16_rn(__fmul_rn(x[i], rinv)));
-      const float a = __bfloat162float(__float2bfloat16_rn(__fmul_rn(xn, w[i])));
-      const float b = __shfl_xor_sync(0xffffffffu, a, 16);          // the element 64 away
-      // first half:  y1 = x1 * cos - x2 * sin      second half:  y2 = x2 * cos + x1 * sin
-      y[i] = lane < 16 ? __fsub_rn(__fmul_rn(a, cosv[i]), __fmul_rn(b, sinv[i]))
-                       : __fadd_rn(__fmul_rn(a, cosv[i]), __fmul_rn(b, sinv[i]));
-    }
-    uint2 outw;
-    outw.x = pack_bf16(y[0], y[1]);
-    outw.y = pack_bf16(y[2], y[3]);
-    if (is_q) {
-      *reinterpret_cast<uint2*>(p.q_out + (static_cast<long long>(tok) * p.H + hd) * 128 + lane * 4) = outw;
-    } else {
-      const int kh = hd - p.H;
-      *reinterpret_cast<uint2*>(p.k_out + (static_cast<long long>(tok) * p.Hkv + kh) * 128 + lane * 4) = outw;
-      if (slot >= 0) *reinterpret_cast<uint2*>(p.k_cache + (slot * p.Hkv + kh) * 128 + lane * 4) = outw;
-    }
+    const bool two = vec2 < n_vec;
+    const int tok2 = two ? static_cast<int>(vec2 / heads) : tok;
+    const int hd2 = two ? static_cast<int>(vec2 - static_cast<long long>(tok2) * heads) : hd;
+    const uint4 raw = *reinterpret_cast<const uint4*>(p.qkv + tok * p.qkv_row_stride + hd * 128 + sub * 8);
+    const uint4 raw2 = *reinterpret_cast<const uint4*>(p.qkv + tok2 * p.qkv_row_stride + hd2 * 128 + sub * 8);
+    qk_one_vector(p, tok, hd, raw, sub, half_mask);
+    if (two) qk_one_vector(p, tok2, hd2, raw2, sub, half_mask);
   }
 }
 
@@ -126,12 +153,12 @@ extern "C" int b200_qk_norm_rope_store(const void* qkv, int64_t qkv_row_stride, 
   if (k_cache && !slot_mapping) return set_error(kErrNullPointer, "qk_norm_rope_store: a cache needs slot_mapping");
   if (k_cache && n_slots <= 0) return set_error(kErrBadShape, "qk_norm_rope_store: n_slots must be positive");
   const long long width = static_cast<long long>(num_heads + 2 * num_kv_heads) * 128;
-  if (qkv_row_stride < width || qkv_row_stride % 4 != 0)
-    return set_error(kErrMisaligned, "qk_norm_rope_store: qkv_row_stride must be >= (H + 2 Hkv) * 128 and a multiple of 4 elements");
+  if (qkv_row_stride < width || qkv_row_stride % 8 != 0)
+    return set_error(kErrMisaligned, "qk_norm_rope_store: qkv_row_stride must be >= (H + 2 Hkv) * 128 and a multiple of 8 elements");
   auto mis = [](const void* ptr, uintptr_t a) { return ptr && (reinterpret_cast<uintptr_t>(ptr) & (a - 1)) != 0; };
-  if (mis(qkv, 8) || mis(q_out, 8) || mis(k_out, 8) || mis(k_cache, 8) || mis(v_cache, 8) || mis(q_weight, 8) ||
-      mis(k_weight, 8) || mis(cos_sin_cache, 16))
-    return set_error(kErrMisaligned, "qk_norm_rope_store: tensors must be 8-byte aligned (the cos/sin table 16-byte)");
+  if (mis(qkv, 16) || mis(q_out, 16) || mis(k_out, 16) || mis(k_cache, 16) || mis(v_cache, 16) || mis(q_weight, 16) ||
+      mis(k_weight, 16) || mis(cos_sin_cache, 16))
+    return set_error(kErrMisaligned, "qk_norm_rope_store: every tensor must be 16-byte aligned");
   QkNormRopeParams p;
   p.qkv = static_cast<const __nv_bfloat16*>(qkv);
   p.qkv_row_stride = qkv_row_stride;
@@ -153,9 +180,9 @@ extern "C" int b200_qk_norm_rope_store(const void* qkv, int64_t qkv_row_stride, 
   const long long n_vec = static_cast<long long>(n_tokens) * (num_heads + 2 * num_kv_heads);
   const int sms = sm_count();
   if (sms <= 0) return set_error(kErrNoDriver, "qk_norm_rope_store: no CUDA device");
-  const long long want = (n_vec + kQkWarps - 1) / kQkWarps;
+  const long long want = (n_vec + kQkThreads / 16 - 1) / (kQkThreads / 16);
   const int grid = static_cast<int>(want < static_cast<long long>(sms) * 8 ? want : static_cast<long long>(sms) * 8);
-  qk_norm_rope_store_kernel<<<grid, kQkWarps * 32, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  qk_norm_rope_store_kernel<<<grid, kQkThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
   g_launches.fetch_add(1);
   return check_cuda(cudaGetLastError(), "qk_norm_rope_store launch");
 }
