@@ -43,6 +43,10 @@ WORKLOADS = {
     # the same batch with a prefix-cache hit (a random whole number of blocks) on the second half of the
     # sequences: the whole batch then reads K/V from the paged cache through block tables
     "prefill_cfg3_prefix": dict(kind="prefill", H=16, Hkv=8, D=128, batch=256, lo=100, hi=1024, seed=3, prefix=True),
+    # the producer side of the layer (QK-norm + rotary embedding + cache store as one kernel) on the
+    # engine's largest prefill batch and on a decode batch; steps rotate over projection buffers larger than L2
+    "producer_prefill": dict(kind="producer", H=16, Hkv=8, D=128, tokens=16384, seed=5, buffers=4),
+    "producer_decode": dict(kind="producer", H=16, Hkv=8, D=128, tokens=256, seed=6, buffers=64),
 }
 BLOCK = 256
 
@@ -420,6 +424,60 @@ def run_prefill(args, w, rank, world, local):
                          "timed_ms": s["timed_ms"], "traffic": None}}
 
 
+def run_producer(args, w, rank, world, local):
+    """QK-norm + RoPE + store: HBM GB/s over the algorithmic bytes (projection row read, q and k written,
+    k and v written to the cache)."""
+    if world != 1:
+        raise SystemExit("the producer workloads are single-GPU workloads")
+    from nanovllm_b200.layers.qk_norm_rope import qk_norm_rope_store
+    from oracle.qk_norm_rope_oracle import rope_cos_sin_cache
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    H, Hkv, D, n = w["H"], w["Hkv"], w["D"], w["tokens"]
+    g = torch.Generator().manual_seed(w["seed"])
+    nb = max(64, 2 * ((n + BLOCK - 1) // BLOCK))
+    qkvs = [torch.randn(n, (H + 2 * Hkv) * D, generator=g).to(torch.bfloat16).to(dev) for _ in range(w["buffers"])]
+    caches = [(torch.zeros(nb, BLOCK, Hkv, D, dtype=torch.bfloat16, device=dev),
+               torch.zeros(nb, BLOCK, Hkv, D, dtype=torch.bfloat16, device=dev)) for _ in range(w["buffers"])]
+    pos = torch.randint(0, 4096, (n,), generator=g, dtype=torch.int64).to(dev)
+    slots = torch.randperm(nb * BLOCK, generator=g)[:n].to(torch.int32).to(dev)
+    qw = (1.0 + 0.1 * torch.randn(D, generator=g)).to(torch.bfloat16).to(dev)
+    kw = (1.0 + 0.1 * torch.randn(D, generator=g)).to(torch.bfloat16).to(dev)
+    cs = rope_cos_sin_cache(D, 4096, 1e6).to(dev)
+    lib = __import__("nanovllm_b200._lib", fromlist=["load"]).load()
+
+    def step(i):
+        kc, vc = caches[i % len(caches)]
+        return qk_norm_rope_store(qkvs[i % len(qkvs)], pos, qw, kw, cs, 1e-6, H, Hkv, kc, vc, slots)
+
+    for i in range(max(args.warmup, 3)):
+        step(i)
+    torch.cuda.synchronize()
+    l0 = lib.b200_launch_count()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sampler = ClockSampler(local)
+    sampler.start()
+    a.record()
+    for i in range(args.steps):
+        step(i)
+    b.record()
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    ms = a.elapsed_time(b) / args.steps
+    nbytes = n * ((H + 2 * Hkv) * D * 2 + H * D * 2 + Hkv * D * 2 + 2 * Hkv * D * 2)
+    pk = peaks()
+    gbs = nbytes / (ms * 1e-3) / 1e9
+    return {"metric": "qk_norm_rope_store_hbm_gbs", "value": round(gbs, 1), "unit": "GB/s", "n_gpus": 1, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": round(ms, 5), "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": args.workload, "tokens": n, "num_heads": H, "num_kv_heads": Hkv, "head_dim": D,
+                       "l2": "steps rotate over %d projection buffers and caches" % w["buffers"],
+                       "bytes_per_step": nbytes},
+            "roofline": {"bound": "hbm", "kernel": "qk_norm_rope_store_kernel", "achieved": round(gbs, 1), "peak": pk["hbm"],
+                         "unit": "GB/s", "frac": round(gbs / pk["hbm"], 4), "peak_source": pk["source"], "traffic": None},
+            "gpu_launches": int(lib.b200_launch_count() - l0), "clocks": clocks}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -440,6 +498,8 @@ def main():
         res = run_reference(args, w, rank, world)
     elif w["kind"] == "decode":
         res = run_decode(args, w, rank, world, local)
+    elif w["kind"] == "producer":
+        res = run_producer(args, w, rank, world, local)
     else:
         res = run_prefill(args, w, rank, world, local)
     if res is not None:

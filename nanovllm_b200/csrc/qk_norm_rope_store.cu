@@ -83,16 +83,25 @@ __device__ __forceinline__ void qk_one_vector(const QkNormRopeParams& p, int tok
   const float rinv = __frsqrt_rn(__fadd_rn(__fdiv_rn(ss, 128.f), p.eps));
   const float cosv[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
   const float sinv[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+  // normalise in fp32, round to bf16, scale by the bf16 weight (rounded to bf16 again); the results are
+  // exact bf16 values, so they travel to the partner lane as packed pairs (4 shuffles instead of 8)
+  uint32_t ap[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const __nv_bfloat162 n2 = __floats2bfloat162_rn(__fmul_rn(x[2 * i], rinv), __fmul_rn(x[2 * i + 1], rinv));
+    ap[i] = pack_bf16(__fmul_rn(__low2float(n2), w[2 * i]), __fmul_rn(__high2float(n2), w[2 * i + 1]));
+  }
   float y[8];
 #pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    // normalise in fp32, round to bf16, scale by the bf16 weight (rounded to bf16 again)
-    const float xn = __bfloat162float(__float2bfloat16_rn(__fmul_rn(x[i], rinv)));
-    const float a = __bfloat162float(__float2bfloat16_rn(__fmul_rn(xn, w[i])));
-    const float b = __shfl_xor_sync(half_mask, a, 8);             // the element 64 away
+  for (int i = 0; i < 4; ++i) {
+    const uint32_t bp = __shfl_xor_sync(half_mask, ap[i], 8);       // the elements 64 away
+    const __nv_bfloat162 a2 = *reinterpret_cast<const __nv_bfloat162*>(&ap[i]);
+    const __nv_bfloat162 b2 = *reinterpret_cast<const __nv_bfloat162*>(&bp);
+    const float a0 = __low2float(a2), a1 = __high2float(a2), b0 = __low2float(b2), b1 = __high2float(b2);
     // first half:  y1 = x1 * cos - x2 * sin      second half:  y2 = x2 * cos + x1 * sin
-    y[i] = sub < 8 ? __fsub_rn(__fmul_rn(a, cosv[i]), __fmul_rn(b, sinv[i]))
-                   : __fadd_rn(__fmul_rn(a, cosv[i]), __fmul_rn(b, sinv[i]));
+    const float t0 = __fmul_rn(b0, sinv[2 * i]), t1 = __fmul_rn(b1, sinv[2 * i + 1]);
+    y[2 * i] = __fadd_rn(__fmul_rn(a0, cosv[2 * i]), sub < 8 ? -t0 : t0);
+    y[2 * i + 1] = __fadd_rn(__fmul_rn(a1, cosv[2 * i + 1]), sub < 8 ? -t1 : t1);
   }
   uint4 outw;
   outw.x = pack_bf16(y[0], y[1]);
@@ -108,7 +117,7 @@ __device__ __forceinline__ void qk_one_vector(const QkNormRopeParams& p, int tok
   }
 }
 
-__global__ void __launch_bounds__(kQkThreads)
+__global__ void __launch_bounds__(kQkThreads, 4)
 qk_norm_rope_store_kernel(const QkNormRopeParams p) {
   // a half-warp owns one head vector: lane j of 16 holds elements [8j, 8j + 8) (one 16-byte access),
   // the rotary partner (element i +- 64) of each of them sits in lane j ^ 8; two vectors are in flight
