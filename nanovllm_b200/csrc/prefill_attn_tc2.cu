@@ -18,7 +18,7 @@
 //   warps 12-15   output warpgroup: takes a finished O out of TMEM, scales it by 1 / row sum and
 //                 sends it out as bf16 through TMA stores (plain stores where a box would overhang
 //                 the sequence), so the softmax warpgroups never stop for output.
-//   (Warps 2-3 idle; setmaxnreg: warpgroup 0 -> 72, softmax -> 184, output -> 72 registers.)
+//   (Warps 2-3 idle; setmaxnreg: warpgroup 0 -> 80, softmax -> 184, output -> 64 registers.)
 // TMEM: S_A [0,128)  S_B [128,256)  O_A [256,384)  O_B [384,512).  Every mbarrier wait is bounded.
 #include <atomic>
 
@@ -221,7 +221,7 @@ prefill_attn_tc2_kernel(const PrefillParams p, const __grid_constant__ CUtensorM
   // Registers move from the light warpgroup to the two softmax warpgroups, which hold a whole
   // 128-column S row (and later the O row) per thread.
   if (warp < 4) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 72;" ::: "memory");
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 80;" ::: "memory");
   if (warp == 0) {
     // ================================ TMA producer ================================
     if (lane == 0) {
@@ -608,7 +608,7 @@ prefill_attn_tc2_kernel(const PrefillParams p, const __grid_constant__ CUtensorM
     }
 #endif
   } else {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 72;" ::: "memory");
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 64;" ::: "memory");
     // ================================ output warpgroup ================================
     const int quarter = warp & 3;
     const int r = quarter * 32 + lane;
