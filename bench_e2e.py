@@ -38,10 +38,9 @@ for _p in (ROOT, _REF):
         sys.path.insert(0, _p)
 
 # Tensor-parallel ranks are spawned processes that re-import this file before they unpickle the
-# model runner, so the layer is installed here, at import time, in every process of the `ours` arm.
-if os.environ.get("B200_E2E_ATTN") == "ours":
-    import nanovllm_b200.integration as _integ
-    _integ.install(fuse_qk_norm_rope=os.environ.get("B200_E2E_FUSE") == "1")
+# model runner, so the layer is installed here, at import time, in every process of the `ours` arm
+# (B200_ATTN_INSTALL set by main() below; unset = the reference's own layer).
+import nanovllm_b200.autoinstall  # noqa: E402,F401
 
 
 def make_model_dir(path: str):
@@ -111,10 +110,10 @@ def main():
                     help="with --attn ours: q_norm + k_norm + rotary_emb + cache store as one kernel")
     args = ap.parse_args()
     want_fuse = "1" if (args.fuse_producer and args.attn == "ours") else "0"
-    if os.environ.get("B200_E2E_ATTN") != args.attn or os.environ.get("B200_E2E_FUSE", "0") != want_fuse:
+    want_env = "" if args.attn == "reference" else ("fused" if want_fuse == "1" else "1")
+    if os.environ.get("B200_ATTN_INSTALL", "") != want_env:
         # set before anything of the engine is imported (and for spawned ranks), then start over
-        os.environ["B200_E2E_ATTN"] = args.attn
-        os.environ["B200_E2E_FUSE"] = want_fuse
+        os.environ["B200_ATTN_INSTALL"] = want_env
         os.execv(sys.executable, [sys.executable] + sys.argv)
 
     import torch

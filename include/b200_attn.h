@@ -121,10 +121,9 @@ int b200_decode_attn_static(const void* q, int64_t q_row_stride, const void* k_c
  * max_seqlen_q / max_seqlen_k are the host-side bounds the caller already has
  * (nanovllm/utils/context.py:9-10).  kernel_variant: 0 = default (the persistent tcgen05 kernel
  * when 128 % (num_heads / num_kv_heads) == 0, else the mma.sync kernel), 1 = force the mma.sync
- * kernel, 2 = force the one-tile-per-CTA tcgen05 kernel, 3 = force the persistent tcgen05 kernel,
- * 4 = force the experimental persistent tcgen05 kernel with 64-key steps (2, 3 and 4 return
- * B200_ERR_BAD_SHAPE if they cannot take the shape).  Launches of the persistent kernels share
- * one device-side ticket counter: do not overlap two of them on one GPU.  The persistent kernel
+ * kernel, 2 = force the tcgen05 kernel (B200_ERR_BAD_SHAPE if it cannot take the shape).  Launches
+ * of the tcgen05 kernel share one device-side ticket counter: do not overlap two of them on one
+ * GPU.  The persistent kernel
  * writes `out` through TMA stores: out must be 16-byte aligned (as every tensor here). */
 int b200_prefill_attn(const void* q, int64_t q_row_stride, const void* k, const void* v, int64_t k_row_stride,
                       int64_t v_row_stride, int64_t total_k, const void* k_cache, const void* v_cache,
@@ -158,10 +157,19 @@ int b200_qk_norm_rope_store(const void* qkv, int64_t qkv_row_stride, const int64
 int64_t b200_launch_count(void);
 
 /* Diagnostic, not for the hot path: synchronises the current device and returns
- * B200_ERR_TIMEOUT if any kernel of this library gave up on a bounded wait since the library
- * was loaded (its output is then undefined), a positive cudaError_t if the device reports an
- * error, else 0. */
+ * B200_ERR_TIMEOUT if any kernel of this library gave up on a bounded wait since the last call
+ * that reported one (the output of that launch is undefined), a positive cudaError_t if the
+ * device reports an error, else 0.  A call that reports a timeout also recovers: it clears the
+ * status words and the prefill kernel's ticket counter, so later launches start clean and the
+ * next call speaks about them only.  What the library cannot reach is the caller-owned decode
+ * workspace: if the failed launch was a decode, zero-fill that workspace again. */
 int b200_device_status(void);
+
+/* Test hook for the recovery path above, never called by the product: synchronises the device and
+ * leaves the library's device-side state as a prefill launch that gave up on a wait would have
+ * left it (status word set, ticket counter stale).  Nothing is launched and no GPU fault is
+ * involved.  The next b200_device_status() must report B200_ERR_TIMEOUT and repair the state. */
+int b200_test_inject_timeout(void);
 
 #ifdef __cplusplus
 }

@@ -36,17 +36,17 @@ SIGNATURES = {
                                           c_int32, c_int32, c_void_p]),
     "b200_launch_count": (c_int64, []),
     "b200_device_status": (c_int32, []),
+    "b200_test_inject_timeout": (c_int32, []),
 }
 
 
 def load():
-    """Loads (building first if the sources are newer) and returns the ctypes library."""
+    """Loads (building first if the library is missing or older than its sources) and returns the
+    ctypes library.  B200_ATTN_REBUILD=1 forces the build."""
     global _lib
     if _lib is not None:
         return _lib
-    path = LIB_PATH
-    if not os.path.exists(path) or os.environ.get("B200_ATTN_REBUILD"):
-        path = build(force=bool(os.environ.get("B200_ATTN_REBUILD")))
+    path = build(force=bool(os.environ.get("B200_ATTN_REBUILD")))
     lib = ctypes.CDLL(path)
     for name, (res, args) in SIGNATURES.items():
         fn = getattr(lib, name)  # AttributeError here = the library does not match the header

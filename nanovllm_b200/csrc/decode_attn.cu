@@ -24,9 +24,6 @@
 //    boundary cuts the (sequence, head), a partial (m, l, unnormalised O) to the workspace; the
 //    last piece to arrive (one atomic counter per (sequence, head), reset by that warp) merges the
 //    partials.  No CTA ever waits for another; every mbarrier wait is bounded.
-#include <atomic>
-#include <cstdlib>
-
 #include "../../include/b200_attn.h"
 #include "kernels.cuh"
 
@@ -49,6 +46,9 @@ constexpr int kWsStatusBytes = 256;  // header: word 0 is the ticket counter of 
 constexpr int kWsCounterInts = kDecMaxBatch * 128;   // arrival counters: fixed region, up to 128 kv heads
 constexpr int kSegRing = kDecStages + 1;   // segment descriptors / query rows in flight
 constexpr int kDecPending = 8;             // partials written but not yet counted, per CTA
+// Geometry of the dynamic tail of the piece scheduler (measured on B200): used from 256 tiles per CTA;
+// one piece of 15 % and four of 3.75 % of a CTA's equal share are handed out through tickets.
+constexpr int kDynFactor = 256, kDynBigPct = 15, kDynSmallPct100 = 375, kDynSmallN = 4;
 static __device__ int g_status_decode = 0;
 
 struct DecodeParams {
@@ -714,6 +714,13 @@ int read_status_decode() {
   return v;
 }
 
+// Only the status word lives in the library; the ticket and arrival counters of an abandoned launch
+// are in the caller's workspace, which the caller has to zero-fill again.
+int reset_state_decode() {
+  const int zero = 0;
+  return check_cuda(cudaMemcpyToSymbol(g_status_decode, &zero, sizeof(int)), "device_status: clearing the decode status word");
+}
+
 // Two hand-off buffers between consumers and the epilogue warp when two CTAs still fit on an SM with them.
 static int decode_merge_buffers(int G) { return G <= 2 ? 2 : 1; }
 
@@ -798,13 +805,9 @@ extern "C" int b200_decode_attn(const void* q, int64_t q_row_stride, const void*
   if (rc) return rc;
 
   const size_t smem = decode_smem_bytes(G);
-  static std::atomic<size_t> configured{0};
-  if (configured.load() < smem) {
-    rc = check_cuda(cudaFuncSetAttribute(decode_attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
-                    "decode_attn: cudaFuncSetAttribute");
-    if (rc) return rc;
-    configured.store(smem);
-  }
+  static std::atomic<size_t> configured[kMaxDevices];
+  rc = ensure_dynamic_smem(reinterpret_cast<const void*>(decode_attn_kernel), smem, configured, "decode_attn: cudaFuncSetAttribute");
+  if (rc) return rc;
 
   unsigned char* ws = static_cast<unsigned char*>(workspace);
   DecodeParams p;
@@ -817,17 +820,10 @@ extern "C" int b200_decode_attn(const void* q, int64_t q_row_stride, const void*
   p.num_blocks = num_blocks;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.n_merge = decode_merge_buffers(G);
-  {
-    auto env_int = [](const char* name, int dflt) { const char* e = getenv(name); return e ? atoi(e) : dflt; };
-    static const int dyn = env_int("B200_DECODE_DYN_FACTOR", 256);
-    static const int big = env_int("B200_DECODE_BIG_PCT", 15);
-    static const int small = env_int("B200_DECODE_SMALL_PCT100", 375);
-    static const int small_n = env_int("B200_DECODE_SMALL_N", 4);
-    p.dyn_factor = dyn;
-    p.big_pct = big;
-    p.small_pct100 = small;
-    p.small_n = small_n < 1 ? 1 : (small_n > 4 ? 4 : small_n);
-  }
+  p.dyn_factor = kDynFactor;
+  p.big_pct = kDynBigPct;
+  p.small_pct100 = kDynSmallPct100;
+  p.small_n = kDynSmallN;
   p.ticket = reinterpret_cast<unsigned int*>(ws);
   p.counters = reinterpret_cast<int*>(ws + kWsStatusBytes);
   p.ws_o = reinterpret_cast<float*>(ws + kWsStatusBytes + static_cast<long long>(kWsCounterInts) * 4);

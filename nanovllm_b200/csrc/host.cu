@@ -37,6 +37,19 @@ int sm_count() {
   return cached[dev];
 }
 
+// cudaFuncAttributeMaxDynamicSharedMemorySize is a per-device attribute: `cache` holds, per device
+// ordinal, the largest size already set for `kernel` there.
+int ensure_dynamic_smem(const void* kernel, size_t bytes, std::atomic<size_t>* cache, const char* what) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices)
+    return set_error(kErrDevice, "%s: device ordinal outside [0, %d)", what, kMaxDevices);
+  if (cache[dev].load(std::memory_order_acquire) >= bytes) return kOk;
+  const int rc = check_cuda(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes)), what);
+  if (rc) return rc;
+  cache[dev].store(bytes, std::memory_order_release);
+  return kOk;
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -108,13 +121,26 @@ int b200_device_status(void) {
     cudaError_t e = cudaGetLastError();
     return b200::check_cuda(e == cudaSuccess ? cudaErrorUnknown : e, "device_status: cudaDeviceSynchronize");
   }
-  if (b200::read_status_decode() || b200::read_status_prefill_mma() || b200::read_status_prefill_tc() ||
-      b200::read_status_prefill_tc2() || b200::read_status_prefill_tc3())
+  const int sd = b200::read_status_decode(), sm = b200::read_status_prefill_mma(), st = b200::read_status_prefill_tc2();
+  if (sd || sm || st) {
+    // Report once and recover: clear the status words and the library's own launch-to-launch state, so that the
+    // next call of this function speaks about later launches only and the next prefill starts from ticket 0.
+    int rc = b200::reset_state_decode();
+    if (!rc) rc = b200::reset_state_prefill_mma();
+    if (!rc) rc = b200::reset_state_prefill_tc2();
+    if (rc) return rc;
     return b200::set_error(b200::kErrTimeout,
-                           "a bounded device-side wait gave up (decode=%d prefill mma=%d tcgen05=%d tcgen05 persistent=%d)",
-                           b200::read_status_decode(), b200::read_status_prefill_mma(), b200::read_status_prefill_tc(),
-                           b200::read_status_prefill_tc2());
+                           "a bounded device-side wait gave up (decode=%d prefill mma.sync=%d prefill tcgen05=%d); the "
+                           "library's own state has been reset, a decode workspace used by the failed call must be "
+                           "zero-filled again by its owner",
+                           sd, sm, st);
+  }
   return b200::kOk;
+}
+
+int b200_test_inject_timeout(void) {
+  if (cudaDeviceSynchronize() != cudaSuccess) return b200::check_cuda(cudaGetLastError(), "test_inject_timeout: cudaDeviceSynchronize");
+  return b200::inject_timeout_prefill_tc2();
 }
 
 }  // extern "C"

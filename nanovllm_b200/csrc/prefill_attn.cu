@@ -27,13 +27,13 @@ extern "C" int b200_prefill_attn(const void* q, int64_t q_row_stride, const void
   if (max_seqlen_q <= 0 || max_seqlen_k <= 0)
     return set_error(kErrBadShape, "prefill_attn: max_seqlen_q/k must be positive");
 
-  if (kernel_variant < 0 || kernel_variant > 4)
-    return set_error(kErrBadShape, "prefill_attn: kernel_variant must be 0 .. 4");
+  if (kernel_variant < 0 || kernel_variant > 2)
+    return set_error(kErrBadShape, "prefill_attn: kernel_variant must be 0 .. 2");
   const bool tc_ok = 128 % G == 0;
-  if (kernel_variant >= 2 && !tc_ok)
+  if (kernel_variant == 2 && !tc_ok)
     return set_error(kErrBadShape, "prefill_attn: the tcgen05 kernel needs 128 %% (num_heads / num_kv_heads) == 0 (got %d)", G);
-  const bool use_tc = kernel_variant >= 2 || (kernel_variant == 0 && tc_ok);
-  const uint32_t kv_box = (use_tc && kernel_variant != 4) ? 128 : 64;
+  const bool use_tc = kernel_variant == 2 || (kernel_variant == 0 && tc_ok);
+  const uint32_t kv_box = use_tc ? 128 : 64;
   CUtensorMap map_k, map_v;
   const bool paged = block_tables != nullptr;
   int rc;
@@ -93,8 +93,6 @@ extern "C" int b200_prefill_attn(const void* q, int64_t q_row_stride, const void
     rc = make_tokens_heads_map(&map_q, q, static_cast<uint64_t>(total_q), num_heads, static_cast<uint64_t>(q_row_stride),
                                static_cast<uint32_t>(p.QT), static_cast<uint32_t>(G));
     if (rc) return rc;
-    if (kernel_variant == 2) return launch_prefill_tc(p, map_q, map_k, map_v, static_cast<cudaStream_t>(stream));
-    if (kernel_variant == 4) return launch_prefill_tc3(p, map_q, map_k, map_v, static_cast<cudaStream_t>(stream));
     // output map of the persistent kernel: boxes of 32 tile rows = (32 / G tokens) x (G heads) x 32 dims
     CUtensorMap map_o = map_q;
     p.out_tma = 32 % G == 0;

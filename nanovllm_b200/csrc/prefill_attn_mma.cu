@@ -262,13 +262,10 @@ prefill_attn_mma_kernel(const PrefillParams p, const __grid_constant__ CUtensorM
 
 int launch_prefill_mma(const PrefillParams& p, const CUtensorMap& map_k, const CUtensorMap& map_v, cudaStream_t stream) {
   const size_t smem = 1024 + static_cast<size_t>(kPfStages) * kPfStageBytes;
-  static std::atomic<int> configured{0};
-  if (!configured.load()) {
-    int rc = check_cuda(cudaFuncSetAttribute(prefill_attn_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
-                        "prefill_attn: cudaFuncSetAttribute");
-    if (rc) return rc;
-    configured.store(1);
-  }
+  static std::atomic<size_t> configured[kMaxDevices];
+  const int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(prefill_attn_mma_kernel), smem, configured,
+                                     "prefill_attn(mma.sync): cudaFuncSetAttribute");
+  if (rc) return rc;
   const long long blocks = static_cast<long long>(p.n_slots) * p.Hkv;
   if (blocks <= 0) return kOk;
   if (blocks > 0x7fffffffLL) return set_error(kErrBadShape, "prefill_attn: too many query tiles");
@@ -281,6 +278,11 @@ int read_status_prefill_mma() {
   int v = 0;
   cudaMemcpyFromSymbol(&v, g_status_prefill_mma, sizeof(int));
   return v;
+}
+
+int reset_state_prefill_mma() {
+  const int zero = 0;
+  return check_cuda(cudaMemcpyToSymbol(g_status_prefill_mma, &zero, sizeof(int)), "device_status: clearing the mma.sync status word");
 }
 
 }  // namespace b200

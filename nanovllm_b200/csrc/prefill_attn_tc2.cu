@@ -20,8 +20,6 @@
 //                 the sequence), so the softmax warpgroups never stop for output.
 //   (Warps 2-3 idle; setmaxnreg: warpgroup 0 -> 80, softmax -> 184, output -> 64 registers.)
 // TMEM: S_A [0,128)  S_B [128,256)  O_A [256,384)  O_B [384,512).  Every mbarrier wait is bounded.
-#include <atomic>
-
 #include "../../include/b200_attn.h"
 #include "kernels.cuh"
 #include "tcgen05.cuh"
@@ -697,19 +695,34 @@ int read_status_prefill_tc2() {
   return v;
 }
 
+// A launch that gave up on a wait never draws its last ticket, so the counter keeps a stale value that
+// would make the next launch skip its first items: clear it together with the status word.
+int reset_state_prefill_tc2() {
+  const int zero = 0;
+  const unsigned int uzero = 0;
+  int rc = check_cuda(cudaMemcpyToSymbol(g_status_prefill_tc2, &zero, sizeof(int)), "device_status: clearing the tcgen05 status word");
+  if (rc) return rc;
+  return check_cuda(cudaMemcpyToSymbol(g_prefill_ticket, &uzero, sizeof(unsigned int)), "device_status: clearing the ticket counter");
+}
+
+int inject_timeout_prefill_tc2() {
+  const int one = 1;
+  const unsigned int stale = 7;
+  int rc = check_cuda(cudaMemcpyToSymbol(g_status_prefill_tc2, &one, sizeof(int)), "inject_timeout: status word");
+  if (rc) return rc;
+  return check_cuda(cudaMemcpyToSymbol(g_prefill_ticket, &stale, sizeof(unsigned int)), "inject_timeout: ticket counter");
+}
+
 // Needs whole query heads groups in a 128-row tile.  The query-block slots are laid out for 2 * QT tokens.
 int launch_prefill_tc2(PrefillParams p, const CUtensorMap& map_q, const CUtensorMap& map_k, const CUtensorMap& map_v,
                        const CUtensorMap& map_o, cudaStream_t stream) {
   p.n_slots = p.total_q / (2 * p.QT) + p.batch;
   const size_t smem = 1024 + static_cast<size_t>(2 + 2 * kT2Ring) * kT2Tile + 8 * 2048 +
                       (p.batch <= kT2MaxSeqSmem ? (p.batch + 1) * 4 : 4) + 64;
-  static std::atomic<size_t> configured{0};
-  if (configured.load() < smem) {
-    int rc = check_cuda(cudaFuncSetAttribute(prefill_attn_tc2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
-                        "prefill_attn(tc2): cudaFuncSetAttribute");
-    if (rc) return rc;
-    configured.store(smem);
-  }
+  static std::atomic<size_t> configured[kMaxDevices];
+  const int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(prefill_attn_tc2_kernel), smem, configured,
+                                     "prefill_attn(tcgen05): cudaFuncSetAttribute");
+  if (rc) return rc;
   const int grid = sm_count();
   if (grid <= 0) return set_error(kErrNoDriver, "prefill_attn: no CUDA device");
   if (static_cast<long long>(p.n_slots) * p.Hkv > 0x7fffffffLL) return set_error(kErrBadShape, "prefill_attn: too many query blocks");

@@ -9,9 +9,8 @@ After install(), `nanovllm.models.qwen3.Qwen3Attention` builds this package's At
 (nanovllm/models/qwen3.py:60-65), the model runner binds the cache onto it
 (nanovllm/engine/model_runner.py:113-117) and the layer reads the engine's own per-step record
 (nanovllm/utils/context.py).  Tensor-parallel ranks are spawned processes that re-import
-everything; set B200_ATTN_INSTALL=1 in the environment and make `nanovllm_b200.autoinstall`
-importable at interpreter start (for instance through a `.pth` file or `sitecustomize`) to install
-there as well -- or start the ranks from a script that calls install() at import time.
+everything: see `nanovllm_b200.autoinstall` (environment variable B200_ATTN_INSTALL) for installing
+the layer in them as well.
 """
 from __future__ import annotations
 

@@ -334,20 +334,20 @@ def _prefill_case(seed, lens, prefix, h, hkv, paged, poison=True):
     return q, kc, vc, cu_q, cu_k, bt, None
 
 
-VARIANTS = {"mma": 1, "tcgen05": 2, "tcgen05_persistent": 3, "tcgen05_persistent_kv64": 4}
+VARIANTS = {"mma": 1, "tcgen05": 2}
 
 
 def _variants(h, hkv):
     g = h // hkv
-    return ["mma"] + (["tcgen05", "tcgen05_persistent", "tcgen05_persistent_kv64"] if 128 % g == 0 else [])
+    return ["mma"] + (["tcgen05"] if 128 % g == 0 else [])
 
 
-@pytest.mark.parametrize("variant", ["mma", "tcgen05", "tcgen05_persistent", "tcgen05_persistent_kv64"])
+@pytest.mark.parametrize("variant", ["mma", "tcgen05"])
 @pytest.mark.parametrize("h,hkv", [(16, 8), (4, 1), (2, 2), (5, 1), (8, 1), (32, 1), (64, 1)])
 def test_prefill_dense_ragged(b200, h, hkv, variant):
     pkg, _ = b200
     if variant not in _variants(h, hkv):
-        pytest.skip("the tcgen05 kernels need 128 % G == 0")
+        pytest.skip("the tcgen05 kernel needs 128 % G == 0")
     lens = [1, 2, 63, 64, 65, 127, 128, 129, 500, 1024, 31]
     q, k, v, cu_q, cu_k, _, fused = _prefill_case(31 + h, lens, [0] * len(lens), h, hkv, paged=False)
     fd = fused.to(DEV)
@@ -362,7 +362,7 @@ def test_prefill_dense_ragged(b200, h, hkv, variant):
     _status_ok()
 
 
-@pytest.mark.parametrize("variant", ["mma", "tcgen05", "tcgen05_persistent", "tcgen05_persistent_kv64"])
+@pytest.mark.parametrize("variant", ["mma", "tcgen05"])
 @pytest.mark.parametrize("h,hkv", [(16, 8), (4, 1), (2, 2)])
 def test_prefill_paged_prefix_poisoned(b200, h, hkv, variant):
     pkg, _ = b200

@@ -109,3 +109,23 @@ print('ok')
 """
     res = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True)
     assert res.returncode == 0 and "ok" in res.stdout, res.stdout + res.stderr
+
+
+@pytest.mark.skipif(not os.path.isdir(os.path.join(REF, "nanovllm")), reason="reference install (baseline/_ref) not present")
+@pytest.mark.parametrize("mode,expect", [("1", True), ("", False)])
+def test_autoinstall_in_a_spawned_child(mode, expect):
+    """What a spawned tensor-parallel rank does: a fresh interpreter that only imports the autoinstall module
+    (as a `.pth` line or the top of the launching script would) ends up with this package's layer under the
+    reference's module name -- and with nothing changed when the variable is unset."""
+    import subprocess
+    code = f"""
+import sys
+sys.path.insert(0, {ROOT!r}); sys.path.insert(0, {REF!r})
+import nanovllm_b200.autoinstall as auto
+import nanovllm_b200.layers.attention as ours
+print(auto.installed, sys.modules.get('nanovllm.layers.attention') is ours)
+"""
+    env = dict(os.environ, B200_ATTN_INSTALL=mode)
+    res = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, env=env)
+    assert res.returncode == 0, res.stdout + res.stderr
+    assert res.stdout.split() == [str(expect), str(expect)]
