@@ -13,9 +13,19 @@ layers' caches (several GB in total), so no step finds its K/V in L2.
 With N > 1 the path is sharded exactly as the reference's tensor parallelism does it -- by KV
 head, identical metadata on every rank, no collective in the data path -- and `value` is the
 bytes all ranks processed divided by the slowest rank's device time ("strong" scaling: the
-global problem is fixed).  `--workload decode_cfg4` runs the Qwen3-8B geometry (32/8 heads,
-batch 512, lengths in [512, 8192]) the same way; `--workload prefill_cfg3` reports prefill
-attention TFLOP/s instead.
+global problem is fixed).
+
+Besides the contract's keys the line carries
+  roofline          the decode kernel alone (CUDA events around every launch) against the measured copy rate
+  e2e               the same steps through Attention.forward with pinned host inputs and a host result
+  hold              the K steps repeated for --hold-seconds, so that the nvidia-smi clock samples of `clocks`
+                    fall inside a loaded region; `ms_x_sm_mhz` = step time x median SM clock
+  cpu_baseline      the CPU restatement (oracle/) on the host cores, same sample as `--impl reference` takes
+  library_baseline  (N = 1) what the reference's own GPU path achieves on the same box in the same run:
+                    flash_attn_with_kvcache / flash_attn_varlen_func / the Triton store_kvcache, called with the
+                    argument pattern of nanovllm/layers/attention.py:33-74 on the same tensors
+  secondary         prefill TFLOP/s on BASELINE config 3 (dense); `secondaries` adds its prefix-cache form and,
+                    at every N, decode on BASELINE config 4 (Qwen3-8B geometry, per-GPU and aggregate GB/s)
 
 `--impl reference` times the reference's algorithm on the host cores (the CPU restatement under
 oracle/, torch with all host threads) on a bounded sample of the same workload.
@@ -34,21 +44,19 @@ import time
 import torch
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
-sys.path.insert(0, ROOT)
+for _p in (ROOT, os.path.join(ROOT, "tests", "golden")):
+    if _p not in sys.path:
+        sys.path.insert(0, _p)
 
-WORKLOADS = {
-    "decode_cfg2": dict(kind="decode", H=16, Hkv=8, D=128, batch=256, lo=100, hi=2048, seed=2, layers=8),
-    "decode_cfg4": dict(kind="decode", H=32, Hkv=8, D=128, batch=512, lo=512, hi=8192, seed=4, layers=3),
-    "prefill_cfg3": dict(kind="prefill", H=16, Hkv=8, D=128, batch=256, lo=100, hi=1024, seed=3),
-    # the same batch with a prefix-cache hit (a random whole number of blocks) on the second half of the
-    # sequences: the whole batch then reads K/V from the paged cache through block tables
-    "prefill_cfg3_prefix": dict(kind="prefill", H=16, Hkv=8, D=128, batch=256, lo=100, hi=1024, seed=3, prefix=True),
-    # the producer side of the layer (QK-norm + rotary embedding + cache store as one kernel) on the
-    # engine's largest prefill batch and on a decode batch; steps rotate over projection buffers larger than L2
-    "producer_prefill": dict(kind="producer", H=16, Hkv=8, D=128, tokens=16384, seed=5, buffers=4),
-    "producer_decode": dict(kind="producer", H=16, Hkv=8, D=128, tokens=256, seed=6, buffers=64),
-}
-BLOCK = 256
+import workloads as wl  # noqa: E402  (seeded input generators; no attention arithmetic)
+
+WORKLOADS = wl.WORKLOADS
+BLOCK = wl.BLOCK
+REF_DIR = os.path.join(ROOT, "baseline", "_ref")
+
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu capture of the
+# library this file ships with (small case of the same kernel, scaled by the tiles a full launch streams)
+TRAFFIC = {"decode_cfg2": 1145381544}
 
 
 def peaks():
@@ -61,7 +69,7 @@ def peaks():
 
 
 class ClockSampler:
-    """nvidia-smi clocks and throttle reasons sampled while the timed region runs."""
+    """nvidia-smi clocks and throttle reasons (read-only query) sampled while the measured regions run."""
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
          "clocks_event_reasons.sw_power_cap")
@@ -76,12 +84,19 @@ class ClockSampler:
             f = tempfile.NamedTemporaryFile("w", suffix=".csv", delete=False)
             self.path = f.name
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.idx), "--query-gpu=" + self.Q,
-                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=f,
+                                          "--format=csv,noheader,nounits", "-lms", "50"], stdout=f,
                                          stderr=subprocess.DEVNULL)
         except Exception:
             self.proc = None
 
-    def stop(self):
+    def count(self):
+        try:
+            return sum(1 for _ in open(self.path))
+        except Exception:
+            return 0
+
+    def stop(self, skip=0):
+        """Summary of the samples taken after the first `skip` lines."""
         out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
         if self.proc is None:
             return out
@@ -99,199 +114,343 @@ class ClockSampler:
             os.unlink(self.path)
         except Exception:
             pass
+        rows = rows[skip:]
         if not rows:
             return out
         sm = [float(r[1]) for r in rows if r[1].replace(".", "").isdigit()]
         mx = [float(r[2]) for r in rows if r[2].replace(".", "").isdigit()]
+        pw = [float(r[3]) for r in rows if r[3].replace(".", "").isdigit()]
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         reasons = [n for j, n in enumerate(names) if any(r[5 + j].lower().startswith("active") for r in rows)]
-        # "under load": the upper half of the samples (idle samples before/after the region read low)
-        load = sorted(sm)[len(sm) // 2:] if sm else []
-        out.update(sm_mhz=statistics.median(load) if load else None, sm_max_mhz=max(mx) if mx else None,
+        out.update(sm_mhz=statistics.median(sm) if sm else None, sm_min_mhz=min(sm) if sm else None,
+                   sm_max_mhz=max(mx) if mx else None, power_w_max=max(pw) if pw else None,
                    reasons=reasons, samples=len(rows))
         return out
 
 
 def dist_env():
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    return rank, world, local
+    return int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("LOCAL_RANK", "0"))
 
 
-def seeded_lens(w):
-    g = torch.Generator().manual_seed(w["seed"])
-    return torch.randint(w["lo"], w["hi"] + 1, (w["batch"],), generator=g, dtype=torch.int32), g
+class Ranks:
+    """Barrier and max-over-ranks for one process per GPU (NCCL only for these two; none in the data path)."""
+
+    def __init__(self, world, dev):
+        self.world, self.dev = world, dev
+
+    def barrier(self):
+        if self.world > 1:
+            torch.distributed.barrier()
+        torch.cuda.synchronize()
+
+    def max(self, x):
+        if self.world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device=self.dev)
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+        return float(t.item())
 
 
 # --------------------------------------------------------------------------------------------
-# decode workload (ours)
+# decode workloads (ours)
 # --------------------------------------------------------------------------------------------
+class DecodeProblem:
+    """One decode workload on this rank: seeded metadata (identical on every rank), this rank's kv heads of
+    `layers` caches, device-resident and pinned-host step inputs."""
+
+    def __init__(self, w, rank, world, dev, layers):
+        from nanovllm_b200.sharding import local_heads
+        self.w, self.dev, self.layers = w, dev, layers
+        self.h, self.hkv = local_heads(w["H"], w["Hkv"], world)
+        self.d, self.b = w["D"], w["batch"]
+        self.scale = self.d ** -0.5
+        self.lens, g = wl.seeded_lens(w)
+        self.bt, self.nb = wl.make_block_tables(self.lens.tolist(), BLOCK, g)
+        self.slots = wl.decode_slots(self.lens.tolist(), self.bt, BLOCK)
+        gd = torch.Generator(device=dev).manual_seed(1000 + rank)
+        self.caches = []
+        for _ in range(layers):
+            kc = torch.randn(self.nb, BLOCK, self.hkv, self.d, device=dev, dtype=torch.bfloat16, generator=gd) * 0.5
+            vc = torch.randn(self.nb, BLOCK, self.hkv, self.d, device=dev, dtype=torch.bfloat16, generator=gd) * 0.5
+            self.caches.append((kc, vc))
+        mk = lambda heads: (torch.randn(self.b, heads, self.d, generator=g) * 0.5).to(torch.bfloat16).pin_memory()
+        self.hq, self.hk, self.hv = mk(self.h), mk(self.hkv), mk(self.hkv)
+        self.h_slots, self.h_lens, self.h_bt = self.slots.pin_memory(), self.lens.pin_memory(), self.bt.pin_memory()
+        self.dq, self.dk, self.dv = self.hq.to(dev), self.hk.to(dev), self.hv.to(dev)
+        self.d_slots, self.d_lens, self.d_bt = self.h_slots.to(dev), self.h_lens.to(dev), self.h_bt.to(dev)
+        self.h_out = torch.empty(self.b, 1, self.h, self.d, dtype=torch.bfloat16).pin_memory()
+        self.dec_bytes = wl.decode_algorithmic_bytes(self.lens, self.h, self.hkv, self.d)
+        self.store_bytes = 2 * (2 * self.b * self.hkv * self.d * 2) + 4 * self.b   # K, V rows read + written, slots read
+        self.step_bytes = self.dec_bytes + self.store_bytes
+
+    def cache_gb(self):
+        return self.layers * 2 * self.nb * BLOCK * self.hkv * self.d * 2 / 1e9
+
+    def step(self, i, ev=None):
+        import nanovllm_b200
+        kc, vc = self.caches[i % self.layers]
+        nanovllm_b200.store_kvcache(self.dk, self.dv, kc, vc, self.d_slots)
+        if ev is not None:
+            ev[0].record()
+        o = nanovllm_b200.decode_attention(self.dq, kc, vc, self.d_lens, self.d_bt, self.scale, self.hkv)
+        if ev is not None:
+            ev[1].record()
+        return o
+
+
+def time_steps(prob, ranks, steps, first):
+    """EXACTLY `steps` steps between barrier + synchronize on both sides; device time, max over ranks (ms)."""
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ranks.barrier()
+    t0.record()
+    for i in range(steps):
+        prob.step(first + i)
+    t1.record()
+    ranks.barrier()
+    return ranks.max(t0.elapsed_time(t1))
+
+
+def time_decode_launches(prob, ranks, steps, first):
+    """The same steps once more with an event pair around every decode launch (kept out of the timed region:
+    an event between the two kernels of a step serialises their programmatic overlap).  Mean ms, max over ranks."""
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+    ranks.barrier()
+    for i in range(steps):
+        prob.step(first + i, evs[i])
+    ranks.barrier()
+    return ranks.max(statistics.mean(a.elapsed_time(b) for a, b in evs))
+
+
 def run_decode(args, w, rank, world, local):
     import torch.distributed as dist
     import nanovllm_b200
     from nanovllm_b200 import _lib
-    from nanovllm_b200.sharding import local_heads
     from nanovllm_b200.utils.context import reset_context, set_context
-    from oracle.attention_oracle import decode_algorithmic_bytes, decode_slots, make_block_tables
 
     dev = torch.device("cuda", local)
     torch.cuda.set_device(dev)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
+    ranks = Ranks(world, dev)
     lib = _lib.load()
-    h, hkv = local_heads(w["H"], w["Hkv"], world)
-    d, b = w["D"], w["batch"]
-    scale = d ** -0.5
-    lens, g = seeded_lens(w)                      # identical metadata on every rank
-    bt, nb = make_block_tables(lens.tolist(), BLOCK, g)
-    slots = decode_slots(lens.tolist(), bt, BLOCK)
-    layers = args.layers or w["layers"]
-    gd = torch.Generator(device=dev).manual_seed(1000 + rank)
-    caches = []
-    for _ in range(layers):
-        kc = torch.randn(nb, BLOCK, hkv, d, device=dev, dtype=torch.bfloat16, generator=gd) * 0.5
-        vc = torch.randn(nb, BLOCK, hkv, d, device=dev, dtype=torch.bfloat16, generator=gd) * 0.5
-        caches.append((kc, vc))
-    att = nanovllm_b200.Attention(h, d, scale, hkv)
-    # host-side step inputs (pinned), as the model runner prepares them
-    hq = (torch.randn(b, h, d, generator=g) * 0.5).to(torch.bfloat16).pin_memory()
-    hk = (torch.randn(b, hkv, d, generator=g) * 0.5).to(torch.bfloat16).pin_memory()
-    hv = (torch.randn(b, hkv, d, generator=g) * 0.5).to(torch.bfloat16).pin_memory()
-    h_slots, h_lens, h_bt = slots.pin_memory(), lens.pin_memory(), bt.pin_memory()
-    dq, dk, dv = hq.to(dev), hk.to(dev), hv.to(dev)
-    d_slots, d_lens, d_bt = h_slots.to(dev), h_lens.to(dev), h_bt.to(dev)
-    h_out = torch.empty(b, 1, h, d, dtype=torch.bfloat16).pin_memory()
-
-    dec_bytes = decode_algorithmic_bytes(lens, h, hkv, d)
-    store_bytes = 2 * (2 * b * hkv * d * 2) + 4 * b          # K and V rows read + written, slots read
-    step_bytes = dec_bytes + store_bytes
-
-    def step_resident(i, ev=None):
-        kc, vc = caches[i % layers]
-        nanovllm_b200.store_kvcache(dk, dv, kc, vc, d_slots)
-        if ev is not None:
-            ev[0].record()
-        o = nanovllm_b200.decode_attention(dq, kc, vc, d_lens, d_bt, scale, hkv)
-        if ev is not None:
-            ev[1].record()
-        return o
-
-    def step_e2e(i):
-        att.k_cache, att.v_cache = caches[i % layers]
-        q_, k_, v_ = hq.to(dev, non_blocking=True), hk.to(dev, non_blocking=True), hv.to(dev, non_blocking=True)
-        set_context(False, slot_mapping=h_slots.to(dev, non_blocking=True),
-                    context_lens=h_lens.to(dev, non_blocking=True), block_tables=h_bt.to(dev, non_blocking=True))
-        o = att(q_, k_, v_)
-        h_out.copy_(o, non_blocking=True)
-        reset_context()
-
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    def max_over_ranks(x):
-        if world == 1:
-            return x
-        t = torch.tensor([x], dtype=torch.float64, device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
-
-    for i in range(args.warmup):
-        step_resident(i)
-    barrier()
     sampler = ClockSampler(local)
     if rank == 0:
-        sampler.start()
+        sampler.start()            # nvidia-smi needs a moment before its first line: start it before the set-up
+    prob = DecodeProblem(w, rank, world, dev, args.layers or w["layers"])
+    att = nanovllm_b200.Attention(prob.h, prob.d, prob.scale, prob.hkv)
+
+    def step_e2e(i):
+        att.k_cache, att.v_cache = prob.caches[i % prob.layers]
+        q_, k_, v_ = (x.to(dev, non_blocking=True) for x in (prob.hq, prob.hk, prob.hv))
+        set_context(False, slot_mapping=prob.h_slots.to(dev, non_blocking=True),
+                    context_lens=prob.h_lens.to(dev, non_blocking=True), block_tables=prob.h_bt.to(dev, non_blocking=True))
+        prob.h_out.copy_(att(q_, k_, v_), non_blocking=True)
+        reset_context()
+
+    for i in range(args.warmup):
+        prob.step(i)
+    ranks.barrier()
     # ---- timed region: K steps, inputs resident in HBM ----
-    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     launches0 = lib.b200_launch_count()
-    barrier()
-    t0.record()
-    for i in range(args.steps):
-        step_resident(args.warmup + i)
-    t1.record()
-    barrier()
+    ms_total = time_steps(prob, ranks, args.steps, args.warmup)
     launches = lib.b200_launch_count() - launches0
-    ms_total = max_over_ranks(t0.elapsed_time(t1))
-    # ---- the same K steps again with an event pair around every decode launch (roofline of the
-    #      dominant kernel; kept out of the region above because an event between the two kernels
-    #      of a step would serialise their programmatic overlap) ----
-    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
-    barrier()
-    for i in range(args.steps):
-        step_resident(args.warmup + i, evs[i])
-    barrier()
-    dec_ms = statistics.mean(a.elapsed_time(b_) for a, b_ in evs)
-    dec_ms = max_over_ranks(dec_ms)
+    dec_ms = time_decode_launches(prob, ranks, args.steps, args.warmup)
     # ---- end to end through the layer's forward, host buffers in, host result out ----
     for i in range(max(3, args.warmup)):
         step_e2e(i)
-    barrier()
+    ranks.barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     wall0 = time.perf_counter()
     e0.record()
     for i in range(args.steps):
         step_e2e(i)
     e1.record()
-    barrier()
+    ranks.barrier()
     wall_ms = (time.perf_counter() - wall0) * 1e3
-    e2e_ms = max_over_ranks(max(e0.elapsed_time(e1), wall_ms))
-    clocks = sampler.stop() if rank == 0 else None
+    e2e_ms = ranks.max(max(e0.elapsed_time(e1), wall_ms))
+    # ---- hold: the K steps repeated until the clock sampler has a loaded region to look at ----
+    skip = sampler.count() if rank == 0 else 0
+    hold_ms, hold_steps, t_hold = [], 0, time.perf_counter()
+    while True:
+        hold_ms.append(time_steps(prob, ranks, args.steps, 0) / args.steps)
+        hold_steps += args.steps
+        flag = torch.tensor([1.0 if time.perf_counter() - t_hold < args.hold_seconds else 0.0], device=dev)
+        if world > 1:
+            dist.broadcast(flag, 0)
+        if flag.item() == 0.0:
+            break
+    clocks = sampler.stop(skip) if rank == 0 else None
     _lib.check(lib.b200_device_status())
 
     ms_per_step = ms_total / args.steps
-    value = world * step_bytes / (ms_per_step * 1e-3) / 1e9
+    value = world * prob.step_bytes / (ms_per_step * 1e-3) / 1e9
     pk = peaks()
-    achieved = dec_bytes / (dec_ms * 1e-3) / 1e9
+    achieved = prob.dec_bytes / (dec_ms * 1e-3) / 1e9
+    hold_med = statistics.median(hold_ms)
     out = {
         "metric": "paged_decode_attn_hbm_gbs", "value": round(value, 1), "unit": "GB/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_per_step, 5), "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": args.workload, "num_heads": w["H"], "num_kv_heads": w["Hkv"], "head_dim": d,
-                   "batch": b, "context_lens": f"uniform[{w['lo']},{w['hi']}] seed {w['seed']}",
-                   "sum_context": int(lens.sum()), "block_size": BLOCK, "num_blocks": nb,
-                   "parallelism": f"tp{world} by kv head ({hkv} kv heads per GPU), no collective",
+        "config": {"workload": args.workload, "num_heads": w["H"], "num_kv_heads": w["Hkv"], "head_dim": prob.d,
+                   "batch": prob.b, "context_lens": f"uniform[{w['lo']},{w['hi']}] seed {w['seed']}",
+                   "sum_context": int(prob.lens.sum()), "block_size": BLOCK, "num_blocks": prob.nb,
+                   "parallelism": f"tp{world} by kv head ({prob.hkv} kv heads per GPU), no collective",
                    "step": "store_kvcache(1 token/seq) + paged decode attention, one layer",
-                   "l2": f"inputs larger than L2: steps rotate over {layers} layer caches "
-                         f"({layers * 2 * nb * BLOCK * hkv * d * 2 / 1e9:.2f} GB per GPU)",
-                   "bytes_per_step_per_gpu": step_bytes},
+                   "l2": f"inputs larger than L2: steps rotate over {prob.layers} layer caches "
+                         f"({prob.cache_gb():.2f} GB per GPU)",
+                   "bytes_per_step_per_gpu": prob.step_bytes},
         "roofline": {"bound": "hbm", "kernel": "decode_attn_kernel", "achieved": round(achieved, 1),
                      "peak": pk["hbm"], "unit": "GB/s", "frac": round(achieved / pk["hbm"], 4),
                      "peak_source": pk["source"], "frac_of_spec_8000": round(achieved / 8000.0, 4),
-                     "algorithmic_bytes_per_launch": dec_bytes, "avg_launch_ms": round(dec_ms, 5),
+                     "algorithmic_bytes_per_launch": prob.dec_bytes, "avg_launch_ms": round(dec_ms, 5),
                      "traffic": TRAFFIC.get(args.workload) if world == 1 else None},
-        "e2e": {"value": round(world * step_bytes / (e2e_ms / args.steps * 1e-3) / 1e9, 1), "unit": "GB/s",
+        "e2e": {"value": round(world * prob.step_bytes / (e2e_ms / args.steps * 1e-3) / 1e9, 1), "unit": "GB/s",
                 "ms_per_step": round(e2e_ms / args.steps, 5),
-                "h2d_bytes_per_step": int(hq.nbytes + hk.nbytes + hv.nbytes + h_slots.nbytes + h_lens.nbytes + h_bt.nbytes),
-                "d2h_bytes_per_step": int(h_out.nbytes),
+                "h2d_bytes_per_step": int(sum(x.nbytes for x in (prob.hq, prob.hk, prob.hv, prob.h_slots, prob.h_lens, prob.h_bt))),
+                "d2h_bytes_per_step": int(prob.h_out.nbytes),
                 "api": "nanovllm_b200.Attention.forward with set_context, pinned host q/k/v/metadata in, host output out"},
-        "gpu_launches": int(launches), "clocks": clocks,
+        "gpu_launches": int(launches),
+        "hold": {"seconds": args.hold_seconds, "steps": hold_steps, "ms_per_step": round(hold_med, 5),
+                 "value": round(world * prob.step_bytes / (hold_med * 1e-3) / 1e9, 1)},
+        "clocks": clocks,
     }
-    if rank == 0 and world == 1:
-        if not args.no_cpu:
-            out["cpu_baseline"] = cpu_decode_baseline(w, sample=64)
-        if not args.no_secondary:
+    if rank == 0 and clocks and clocks.get("sm_mhz"):
+        out["hold"]["ms_x_sm_mhz"] = round(hold_med * clocks["sm_mhz"], 2)
+    if rank == 0 and world == 1 and not args.no_cpu:
+        out["cpu_baseline"] = cpu_decode_baseline(w, sample=cpu_sample_size(w, args.steps))
+    if not args.no_secondary:
+        if world == 1:
+            out["library_baseline"] = library_baseline(dev, prob)
+        del prob, att
+        torch.cuda.empty_cache()
+        secondaries = []
+        if world == 1:
             out["secondary"] = secondary_prefill(dev)
+            secondaries.append(secondary_prefill(dev, workload="prefill_cfg3_prefix"))
+        if args.workload != "decode_cfg4":
+            secondaries.append(secondary_decode(args, "decode_cfg4", rank, world, dev, ranks))
+        out["secondaries"] = secondaries
     if world > 1:
         dist.destroy_process_group()
     return out if rank == 0 else None
 
 
-# dram bytes per launch of the dominant kernel from the committed ncu captures (profiles/), or None
-TRAFFIC = {"decode_cfg2": 1145381544}   # dram read + write per launch, profiles/decode_attn_kernel_decode_cfg2.md
+def secondary_decode(args, name, rank, world, dev, ranks, steps=30):
+    """Another decode configuration, sharded the same way: per-GPU and aggregate GB/s, kernel roofline."""
+    w = WORKLOADS[name]
+    prob = DecodeProblem(w, rank, world, dev, w["layers"])
+    for i in range(3):
+        prob.step(i)
+    ms = time_steps(prob, ranks, steps, 3) / steps
+    dec_ms = time_decode_launches(prob, ranks, steps, 3)
+    pk = peaks()
+    per_gpu = prob.step_bytes / (ms * 1e-3) / 1e9
+    kern = prob.dec_bytes / (dec_ms * 1e-3) / 1e9
+    out = {"metric": "paged_decode_attn_hbm_gbs", "workload": name, "n_gpus": world, "steps": steps,
+           "num_heads": w["H"], "num_kv_heads": w["Hkv"], "batch": w["batch"],
+           "context_lens": f"uniform[{w['lo']},{w['hi']}] seed {w['seed']}",
+           "parallelism": f"tp{world} by kv head ({prob.hkv} kv heads per GPU), no collective",
+           "value": round(world * per_gpu, 1), "per_gpu": round(per_gpu, 1), "unit": "GB/s", "ms_per_step": round(ms, 5),
+           "kernel_gbs": round(kern, 1), "kernel_ms": round(dec_ms, 5), "frac": round(kern / pk["hbm"], 4),
+           "peak": pk["hbm"], "peak_source": pk["source"], "frac_of_spec_8000": round(kern / 8000.0, 4),
+           "cache_gb_per_gpu": round(prob.cache_gb(), 2)}
+    del prob
+    torch.cuda.empty_cache()
+    return out
+
+
+# --------------------------------------------------------------------------------------------
+# the reference's own GPU path on the same box (harness only: flash_attn and Triton never enter the product)
+# --------------------------------------------------------------------------------------------
+def _event_ms(fn, iters, warm=3):
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(iters):
+        fn()
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) / iters
+
+
+def library_baseline(dev, prob, iters=20):
+    """flash_attn_with_kvcache, flash_attn_varlen_func and the Triton store_kvcache with the argument pattern of
+    nanovllm/layers/attention.py:33-74, on the tensors of this run (decode: rotating over the same layer caches)."""
+    out = {"what": "the reference's GPU path (flash_attn + Triton) on this box, same tensors, CUDA events"}
+    try:
+        import flash_attn
+        from flash_attn import flash_attn_varlen_func, flash_attn_with_kvcache
+        out["flash_attn"] = flash_attn.__version__
+    except Exception as e:  # noqa: BLE001
+        return {"unavailable": f"flash_attn does not import here: {e!r}"[:200]}
+    try:
+        state = {"i": 0}
+
+        def dec():
+            kc, vc = prob.caches[state["i"] % prob.layers]
+            state["i"] += 1
+            return flash_attn_with_kvcache(prob.dq.unsqueeze(1), kc, vc, cache_seqlens=prob.d_lens, block_table=prob.d_bt,
+                                           softmax_scale=prob.scale, causal=True)
+        ms = _event_ms(dec, iters)
+        out["decode_ms"] = round(ms, 5)
+        out["decode_gbs"] = round(prob.dec_bytes / (ms * 1e-3) / 1e9, 1)
+    except Exception as e:  # noqa: BLE001
+        out["decode_error"] = repr(e)[:200]
+    try:
+        if REF_DIR not in sys.path:
+            sys.path.insert(0, REF_DIR)
+        from nanovllm.layers.attention import store_kvcache as ref_store   # the reference's Triton kernel, unmodified
+        state2 = {"i": 0}
+
+        def st():
+            kc, vc = prob.caches[state2["i"] % prob.layers]
+            state2["i"] += 1
+            ref_store(prob.dk, prob.dv, kc, vc, prob.d_slots)
+        out["store_us"] = round(_event_ms(st, iters) * 1e3, 2)
+        import nanovllm_b200
+        state3 = {"i": 0}
+
+        def st_ours():
+            kc, vc = prob.caches[state3["i"] % prob.layers]
+            state3["i"] += 1
+            nanovllm_b200.store_kvcache(prob.dk, prob.dv, kc, vc, prob.d_slots)
+        out["store_us_ours"] = round(_event_ms(st_ours, iters) * 1e3, 2)
+    except Exception as e:  # noqa: BLE001
+        out["store_error"] = repr(e)[:200]
+    try:
+        w, lens, cu, q, k, v = prefill_inputs(dev)
+        mx = int(lens.max())
+        flops = wl.prefill_algorithmic_flops(lens.tolist(), lens.tolist(), w["H"], w["D"])
+        ms = _event_ms(lambda: flash_attn_varlen_func(q, k, v, max_seqlen_q=mx, cu_seqlens_q=cu, max_seqlen_k=mx,
+                                                      cu_seqlens_k=cu, softmax_scale=w["D"] ** -0.5, causal=True,
+                                                      block_table=None), 10)
+        out["prefill_ms"] = round(ms, 4)
+        out["prefill_tflops"] = round(flops / (ms * 1e-3) / 1e12, 1)
+        del q, k, v
+        lq, lens, cu_q, cu_k, bt, q, kc, vc = prefill_prefix_inputs(dev, WORKLOADS["prefill_cfg3_prefix"])
+        flops = wl.prefill_algorithmic_flops(lq.tolist(), lens.tolist(), w["H"], w["D"])
+        ms = _event_ms(lambda: flash_attn_varlen_func(q, kc, vc, max_seqlen_q=int(lq.max()), cu_seqlens_q=cu_q,
+                                                      max_seqlen_k=int(lens.max()), cu_seqlens_k=cu_k,
+                                                      softmax_scale=w["D"] ** -0.5, causal=True, block_table=bt), 10)
+        out["prefill_prefix_ms"] = round(ms, 4)
+        out["prefill_prefix_tflops"] = round(flops / (ms * 1e-3) / 1e12, 1)
+    except Exception as e:  # noqa: BLE001
+        out["prefill_error"] = repr(e)[:200]
+    torch.cuda.empty_cache()
+    return out
 
 
 # --------------------------------------------------------------------------------------------
 # CPU legs: the oracle timed on the host cores
 # --------------------------------------------------------------------------------------------
 def cpu_decode_baseline(w, sample, repeats=1):
-    from oracle.attention_oracle import decode_algorithmic_bytes, decode_attn_ref, make_block_tables
+    from oracle.attention_oracle import decode_attn_ref
     torch.set_num_threads(os.cpu_count() or 1)
-    lens, g = seeded_lens(w)
+    lens, g = wl.seeded_lens(w)
     lens = lens[:sample]
-    bt, nb = make_block_tables(lens.tolist(), BLOCK, g)
+    bt, nb = wl.make_block_tables(lens.tolist(), BLOCK, g)
     hkv, h, d = w["Hkv"], w["H"], w["D"]
     kc = (torch.randn(nb, BLOCK, hkv, d, generator=g) * 0.5).to(torch.bfloat16)
     vc = (torch.randn(nb, BLOCK, hkv, d, generator=g) * 0.5).to(torch.bfloat16)
@@ -301,10 +460,23 @@ def cpu_decode_baseline(w, sample, repeats=1):
     for _ in range(repeats):
         decode_attn_ref(q, kc, vc, lens, bt, d ** -0.5)
     dt = (time.perf_counter() - t0) / repeats
-    nbytes = decode_algorithmic_bytes(lens, h, hkv, d)
+    nbytes = wl.decode_algorithmic_bytes(lens, h, hkv, d)
     return {"value": round(nbytes / dt / 1e9, 3), "unit": "GB/s", "cores": torch.get_num_threads(), "kind": "port",
             "sample": f"first {len(lens)} of {w['batch']} sequences of the workload, fp32 math on bf16 data, "
                       f"{dt:.2f} s per pass", "seconds_per_pass": dt, "bytes_per_pass": nbytes}
+
+
+_cpu_sample_cache = {}
+
+
+def cpu_sample_size(w, steps):
+    """Sequences per CPU pass, the same rule for the `ours` arm's cpu_baseline and for `--impl reference`: the
+    whole batch if `steps` passes of it take under about a minute on this host, else as many as do."""
+    key = (w["seed"], steps)
+    if key not in _cpu_sample_cache:
+        per_seq = cpu_decode_baseline(w, sample=8)["seconds_per_pass"] / 8
+        _cpu_sample_cache[key] = int(max(2, min(w["batch"], 60.0 / max(steps, 1) / max(per_seq, 1e-6))))
+    return _cpu_sample_cache[key]
 
 
 def run_reference(args, w, rank, world):
@@ -312,11 +484,8 @@ def run_reference(args, w, rank, world):
         return None
     if w["kind"] != "decode":
         raise SystemExit("--impl reference supports the decode workloads")
-    # a step = the decode attention of the first `sample` sequences of the workload; the sample is sized
-    # from a short probe so that the K timed steps take about 40 s in total on this host
-    probe = cpu_decode_baseline(w, sample=8)
-    per_seq = probe["seconds_per_pass"] / 8
-    sample = int(max(2, min(w["batch"], 40.0 / max(args.steps, 1) / max(per_seq, 1e-6))))
+    # a step = the decode attention of the first `sample` sequences of the workload on the host cores
+    sample = cpu_sample_size(w, args.steps)
     for _ in range(min(args.warmup, 2)):
         cpu_decode_baseline(w, sample=min(sample, 8))
     res = cpu_decode_baseline(w, sample=sample, repeats=args.steps)
@@ -339,9 +508,8 @@ def run_reference(args, w, rank, world):
 # --------------------------------------------------------------------------------------------
 def prefill_inputs(dev, w=None):
     w = w or WORKLOADS["prefill_cfg3"]
-    lens, g = seeded_lens(w)
-    cu = torch.zeros(w["batch"] + 1, dtype=torch.int32)
-    cu[1:] = lens.cumsum(0)
+    lens, g = wl.seeded_lens(w)
+    cu = wl.cu_seqlens(lens)
     t = int(cu[-1])
     gd = torch.Generator(device=dev).manual_seed(77)
     q = torch.randn(t, w["H"], w["D"], device=dev, dtype=torch.bfloat16, generator=gd)
@@ -352,19 +520,11 @@ def prefill_inputs(dev, w=None):
 
 def prefill_prefix_inputs(dev, w):
     """Paged form: every key comes from the cache; the second half of the batch has a cached prefix."""
-    from oracle.attention_oracle import make_block_tables
-    lens, g = seeded_lens(w)
-    n = w["batch"]
-    prefix = torch.zeros(n, dtype=torch.int32)
-    for i in range(n // 2, n):
-        mxb = (int(lens[i]) - 1) // BLOCK
-        prefix[i] = BLOCK * int(torch.randint(0, mxb + 1, (1,), generator=g)) if mxb > 0 else 0
+    lens, g = wl.seeded_lens(w)
+    prefix = wl.cached_prefixes(lens, g)
     lq = lens - prefix
-    cu_q = torch.zeros(n + 1, dtype=torch.int32)
-    cu_q[1:] = lq.cumsum(0)
-    cu_k = torch.zeros(n + 1, dtype=torch.int32)
-    cu_k[1:] = lens.cumsum(0)
-    bt, nb = make_block_tables(lens.tolist(), BLOCK, g)
+    cu_q, cu_k = wl.cu_seqlens(lq), wl.cu_seqlens(lens)
+    bt, nb = wl.make_block_tables(lens.tolist(), BLOCK, g)
     gd = torch.Generator(device=dev).manual_seed(78)
     q = torch.randn(int(cu_q[-1]), w["H"], w["D"], device=dev, dtype=torch.bfloat16, generator=gd)
     kc = torch.randn(nb, BLOCK, w["Hkv"], w["D"], device=dev, dtype=torch.bfloat16, generator=gd)
@@ -374,30 +534,20 @@ def prefill_prefix_inputs(dev, w):
 
 def secondary_prefill(dev, iters=10, workload="prefill_cfg3"):
     import nanovllm_b200
-    from oracle.attention_oracle import prefill_algorithmic_flops
     w = WORKLOADS[workload]
     if w.get("prefix"):
         lq, lens, cu_q, cu_k, bt, q, kc, vc = prefill_prefix_inputs(dev, w)
-        flops = prefill_algorithmic_flops(lq.tolist(), lens.tolist(), w["H"], w["D"])
+        flops = wl.prefill_algorithmic_flops(lq.tolist(), lens.tolist(), w["H"], w["D"])
         f = lambda: nanovllm_b200.prefill_attention(q, kc, vc, cu_q, cu_k, int(lq.max()), int(lens.max()), w["D"] ** -0.5,
                                                     w["Hkv"], block_tables=bt)
         label = "prefill_cfg3_prefix (256 seqs, len uniform[100,1024], second half with a cached whole-block prefix, paged K/V)"
     else:
         w, lens, cu, q, k, v = prefill_inputs(dev, w)
-        flops = prefill_algorithmic_flops(lens.tolist(), lens.tolist(), w["H"], w["D"])
+        flops = wl.prefill_algorithmic_flops(lens.tolist(), lens.tolist(), w["H"], w["D"])
         mx = int(lens.max())
         f = lambda: nanovllm_b200.prefill_attention(q, k, v, cu, cu, mx, mx, w["D"] ** -0.5, w["Hkv"])
         label = "prefill_cfg3 (256 seqs, len uniform[100,1024], dense K/V, causal)"
-    for _ in range(3):
-        f()
-    torch.cuda.synchronize()
-    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    a.record()
-    for _ in range(iters):
-        f()
-    b.record()
-    torch.cuda.synchronize()
-    ms = a.elapsed_time(b) / iters
+    ms = _event_ms(f, iters)
     pk = peaks()
     tf = flops / (ms * 1e-3) / 1e12
     # a timed region of a few launches runs at burst clocks; a long one settles under the power cap,
@@ -430,7 +580,6 @@ def run_producer(args, w, rank, world, local):
     if world != 1:
         raise SystemExit("the producer workloads are single-GPU workloads")
     from nanovllm_b200.layers.qk_norm_rope import qk_norm_rope_store
-    from oracle.qk_norm_rope_oracle import rope_cos_sin_cache
     dev = torch.device("cuda", local)
     torch.cuda.set_device(dev)
     H, Hkv, D, n = w["H"], w["Hkv"], w["D"], w["tokens"]
@@ -443,7 +592,7 @@ def run_producer(args, w, rank, world, local):
     slots = torch.randperm(nb * BLOCK, generator=g)[:n].to(torch.int32).to(dev)
     qw = (1.0 + 0.1 * torch.randn(D, generator=g)).to(torch.bfloat16).to(dev)
     kw = (1.0 + 0.1 * torch.randn(D, generator=g)).to(torch.bfloat16).to(dev)
-    cs = rope_cos_sin_cache(D, 4096, 1e6).to(dev)
+    cs = wl.rope_table(D, 4096, 1e6).to(dev)
     lib = __import__("nanovllm_b200._lib", fromlist=["load"]).load()
 
     def step(i):
@@ -485,9 +634,11 @@ def main():
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="decode_cfg2", choices=list(WORKLOADS))
-    ap.add_argument("--no-secondary", action="store_true", help="skip the prefill side measurement")
+    ap.add_argument("--no-secondary", action="store_true", help="skip the library baseline and the secondary workloads")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--layers", type=int, default=0, help="layer caches the steps rotate over (0 = workload default)")
+    ap.add_argument("--hold-seconds", type=float, default=2.0,
+                    help="how long the steps are repeated after the timed region for the clock samples")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     rank, world, local = dist_env()

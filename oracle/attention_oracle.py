@@ -28,7 +28,6 @@ tests/golden/ together with the script that produced them (tests/golden/make_gol
 """
 from __future__ import annotations
 
-import math
 from dataclasses import dataclass
 
 import torch
@@ -161,67 +160,3 @@ class AttentionRef:
                                     self.scale, context.block_tables)
         return decode_attn_ref(q, k_cache, v_cache, context.context_lens,
                                context.block_tables, self.scale)
-
-
-# ----------------------------------------------------------------------------------------------
-# Algorithmic work (the numbers roofline fractions are computed from)
-# ----------------------------------------------------------------------------------------------
-
-def decode_algorithmic_bytes(context_lens, num_heads, num_kv_heads, head_dim, elem_bytes=2):
-    """K and V of every context token once, plus q read and o written."""
-    total = int(torch.as_tensor(context_lens).to(torch.int64).sum())
-    b = len(context_lens)
-    return total * num_kv_heads * head_dim * 2 * elem_bytes + 2 * b * num_heads * head_dim * elem_bytes
-
-
-def prefill_algorithmic_flops(lens_q, lens_k, num_heads, head_dim):
-    """4*D flops per visible (query, key) pair per head (2*D for QK^T and 2*D for PV)."""
-    pairs = 0
-    for lq, lk in zip(lens_q, lens_k):
-        lq, lk = int(lq), int(lk)
-        pairs += lq * (lk - lq) + lq * (lq + 1) // 2
-    return 4 * head_dim * num_heads * pairs
-
-
-# ----------------------------------------------------------------------------------------------
-# Seeded workloads shared by tests, bench and the golden generator
-# ----------------------------------------------------------------------------------------------
-
-def make_block_tables(lens, block_size, generator, slack=8, num_blocks=None):
-    """Scattered block tables: a seeded random permutation of block ids, rows padded with -1
-    (nanovllm/engine/model_runner.py:119-123)."""
-    lens = [int(x) for x in lens]
-    nblk = [(n + block_size - 1) // block_size for n in lens]
-    total = sum(nblk)
-    nb = num_blocks if num_blocks is not None else total + slack
-    assert nb >= total
-    perm = torch.randperm(nb, generator=generator)[:total].to(torch.int32)
-    width = max(max(nblk), 1)
-    bt = torch.full((len(lens), width), -1, dtype=torch.int32)
-    o = 0
-    for i, n in enumerate(nblk):
-        bt[i, :n] = perm[o:o + n]
-        o += n
-    return bt, nb
-
-
-def decode_slots(lens, block_tables, block_size):
-    """Slot of the token appended this step (nanovllm/engine/model_runner.py:172)."""
-    out = []
-    for i, n in enumerate(lens):
-        n = int(n)
-        out.append(int(block_tables[i, (n - 1) // block_size]) * block_size + (n - 1) % block_size)
-    return torch.tensor(out, dtype=torch.int32)
-
-
-def prefill_slots(lens_k, prefix, block_tables, block_size):
-    """Slots of the uncached tokens of every sequence (nanovllm/engine/model_runner.py:146-152)."""
-    out = []
-    for i, (lk, p) in enumerate(zip(lens_k, prefix)):
-        for t in range(int(p), int(lk)):
-            out.append(int(block_tables[i, t // block_size]) * block_size + t % block_size)
-    return torch.tensor(out, dtype=torch.int32)
-
-
-def default_scale(head_dim):
-    return 1.0 / math.sqrt(head_dim)

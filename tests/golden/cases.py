@@ -21,8 +21,8 @@ _ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__
 if _ROOT not in sys.path:
     sys.path.insert(0, _ROOT)
 
-from oracle.attention_oracle import (Context, decode_slots, default_scale,  # noqa: E402
-                                     make_block_tables, prefill_slots)
+from oracle.attention_oracle import Context  # noqa: E402
+from workloads import decode_slots, default_scale, make_block_tables, prefill_slots  # noqa: E402
 
 BLOCK = 256
 DT = torch.bfloat16

@@ -10,8 +10,9 @@ import pytest
 import torch
 
 import cases
-from oracle.attention_oracle import (AttentionRef, Context, decode_attn_ref, decode_slots, default_scale,
-                                     make_block_tables, prefill_attn_ref, prefill_slots, store_kvcache_ref)
+import workloads
+from oracle.attention_oracle import AttentionRef, Context, decode_attn_ref, prefill_attn_ref, store_kvcache_ref
+from workloads import decode_slots, default_scale, make_block_tables, prefill_slots
 
 pytestmark = pytest.mark.gpu
 
@@ -54,7 +55,6 @@ def test_golden_cases(b200, name):
     pkg, ctxmod = b200
     gold = torch.load(GOLD, weights_only=True)[name]
     spec, t, ctx = cases.build_case(name)
-    same_inputs = cases.inputs_sha(t, ctx) == gold["inputs_sha"]
     d = {k: v.to(DEV) for k, v in t.items()}
     att = pkg.Attention(spec["H"], spec["D"], cases.scale_of(spec), spec["Hkv"])
     if "k_cache" in d:
@@ -73,12 +73,16 @@ def test_golden_cases(b200, name):
     if "k_cache" in t:
         assert torch.equal(d["k_cache"].cpu().view(torch.int16), t["k_cache"].view(torch.int16))
         assert torch.equal(d["v_cache"].cpu().view(torch.int16), t["v_cache"].view(torch.int16))
-    if same_inputs:
-        _close(out, gold["out"])
-        if "k_cache" in t:
-            assert cases.tensor_sha(d["k_cache"]) == gold["k_cache_sha"]
-            assert cases.tensor_sha(d["v_cache"]) == gold["v_cache_sha"]
     _status_ok()
+    # against what the reference module itself produced (Triton store + flash_attn on a B200) for these inputs
+    if cases.inputs_sha(t, ctx) != gold["inputs_sha"]:
+        pytest.skip("REFERENCE OUTPUTS NOT COMPARED: this torch build draws other seeded inputs than the one "
+                    "tests/golden/golden.pt was made with (the oracle comparison above passed); regenerate the "
+                    "file with tests/golden/make_golden.py")
+    _close(out, gold["out"])
+    if "k_cache" in t:
+        assert cases.tensor_sha(d["k_cache"]) == gold["k_cache_sha"]
+        assert cases.tensor_sha(d["v_cache"]) == gold["v_cache_sha"]
 
 
 # ------------------------------------------------------------------------------------------------
@@ -191,7 +195,7 @@ def test_decode_large_batch_eager_path(b200):
 
 
 def test_decode_config2_shape_repeatable(b200):
-    """BASELINE config 2 at full size; oracle on a sample of rows; two runs bit-identical."""
+    """BASELINE config 2 at full size; oracle on all 256 rows; two runs agree."""
     pkg, _ = b200
     g = torch.Generator().manual_seed(2)
     lens = torch.randint(100, 2049, (256,), generator=g).tolist()
@@ -200,22 +204,35 @@ def test_decode_config2_shape_repeatable(b200):
     o1 = pkg.decode_attention(qd, kd, vd, cd, bd, default_scale(128), 8)
     o2 = pkg.decode_attention(qd, kd, vd, cd, bd, default_scale(128), 8)
     torch.cuda.synchronize()
-    rows = list(range(0, 256, 16))
-    want = decode_attn_ref(q[rows], kc, vc, cl[rows], bt[rows], default_scale(128))
-    _close(o1[rows], want)
+    _close(o1, decode_attn_ref(q, kc, vc, cl, bt, default_scale(128)))
     # the split points do not depend on timing, but the merge order of partials does not either
     _close(o1, o2)
     _status_ok()
 
 
-def test_decode_long_streams_dynamic_tail(b200):
-    """Large enough (>= 256 tiles per CTA) for the ticket-scheduled tail pieces: Qwen3-8B geometry at
-    TP2, batch 512, lengths U[512, 8192] (4.7 GB of cache).  The cache is built on the GPU; the oracle runs on a
-    sample of sequences whose blocks are copied back."""
+def _oracle_one_paged_decode(q_row, kc, vc, bt_row, n, hkv, d, bs):
+    """Oracle on one sequence of a cache that lives on the GPU: only that sequence's blocks are copied back."""
+    nblk = (n + bs - 1) // bs
+    idx = bt_row[:nblk].long().to(DEV)
+    k = kc[idx].reshape(-1, hkv, d)[:n].cpu()
+    v = vc[idx].reshape(-1, hkv, d)[:n].cpu()
+    pad = nblk * bs - n
+    kcs = torch.cat([k, torch.zeros(pad, hkv, d, dtype=k.dtype)]).view(nblk, bs, hkv, d)
+    vcs = torch.cat([v, torch.zeros(pad, hkv, d, dtype=v.dtype)]).view(nblk, bs, hkv, d)
+    small_bt = torch.arange(nblk, dtype=torch.int32).view(1, -1)
+    return decode_attn_ref(q_row.cpu(), kcs, vcs, torch.tensor([n], dtype=torch.int32), small_bt, default_scale(d))
+
+
+@pytest.mark.parametrize("tp", [1, 2])
+def test_decode_config4_full_size(b200, tp):
+    """BASELINE config 4 at full size: Qwen3-8B geometry (32 query / 8 kv heads at TP1, 16 / 4 at TP2), batch 512,
+    lengths U[512, 8192] (9.4 GB of cache at TP1).  Large enough (>= 256 tiles per CTA) for the ticket-scheduled
+    tail pieces.  The cache is built on the GPU; the oracle runs on a sample of sequences whose blocks are
+    copied back."""
     pkg, _ = b200
-    h, hkv, d, bs = 16, 4, 128, 256
-    g = torch.Generator().manual_seed(91)
-    lens = torch.randint(512, 8193, (512,), generator=g, dtype=torch.int32)
+    w = workloads.WORKLOADS["decode_cfg4"]
+    h, hkv, d, bs = w["H"] // tp, w["Hkv"] // tp, w["D"], 256
+    lens, g = workloads.seeded_lens(w)
     bt, nb = make_block_tables(lens.tolist(), bs, g)
     gd = torch.Generator(device=DEV).manual_seed(92)
     kc = torch.randn(nb, bs, hkv, d, device=DEV, dtype=torch.bfloat16, generator=gd)
@@ -228,18 +245,10 @@ def test_decode_long_streams_dynamic_tail(b200):
     torch.cuda.synchronize()
     assert torch.isfinite(out1.float()).all()
     _close(out1, out2)                      # piece assignment differs from run to run; results agree
-    for i in list(range(0, 512, 47)) + [511]:
-        n = int(lens[i])
-        nblk = (n + bs - 1) // bs
-        idx = bt[i, :nblk].long().to(DEV)
-        k = kc[idx].reshape(-1, hkv, d)[:n].cpu()
-        v = vc[idx].reshape(-1, hkv, d)[:n].cpu()
-        small_bt = torch.arange(nblk, dtype=torch.int32).view(1, -1)
-        pad = nblk * bs - n
-        kcs = torch.cat([k, torch.zeros(pad, hkv, d, dtype=k.dtype)]).view(nblk, bs, hkv, d)
-        vcs = torch.cat([v, torch.zeros(pad, hkv, d, dtype=v.dtype)]).view(nblk, bs, hkv, d)
-        want = decode_attn_ref(q[i:i + 1].cpu(), kcs, vcs, lens[i:i + 1], small_bt, default_scale(d))
-        _close(out1[i:i + 1], want)
+    for i in list(range(0, 512, 31)) + [511]:
+        _close(out1[i:i + 1], _oracle_one_paged_decode(q[i:i + 1], kc, vc, bt[i], int(lens[i]), hkv, d, bs))
+    del kc, vc
+    torch.cuda.empty_cache()
     _status_ok()
 
 
@@ -407,6 +416,40 @@ def test_prefill_config3_scale_and_many_sequences(b200):
     _status_ok()
 
 
+def test_prefill_config3_prefix_half_full_size(b200):
+    """BASELINE config 3 in its prefix-cache form at full size: 256 sequences U[100, 1024], the second half with a
+    cached prefix of a random whole number of blocks, so the whole batch reads K/V from the paged cache
+    (nanovllm/engine/model_runner.py:153-154).  Oracle on 32 sequences, half of them with a prefix."""
+    pkg, _ = b200
+    w = workloads.WORKLOADS["prefill_cfg3_prefix"]
+    h, hkv, d, bs = w["H"], w["Hkv"], w["D"], 256
+    lens, g = workloads.seeded_lens(w)
+    prefix = workloads.cached_prefixes(lens, g)
+    assert int((prefix > 0).sum()) >= 64
+    lq = lens - prefix
+    cu_q, cu_k = workloads.cu_seqlens(lq), workloads.cu_seqlens(lens)
+    bt, nb = make_block_tables(lens.tolist(), bs, g)
+    gd = torch.Generator(device=DEV).manual_seed(78)
+    q = torch.randn(int(cu_q[-1]), h, d, device=DEV, dtype=torch.bfloat16, generator=gd)
+    kc = torch.randn(nb, bs, hkv, d, device=DEV, dtype=torch.bfloat16, generator=gd)
+    vc = torch.randn(nb, bs, hkv, d, device=DEV, dtype=torch.bfloat16, generator=gd)
+    out = pkg.prefill_attention(q, kc, vc, cu_q.to(DEV), cu_k.to(DEV), int(lq.max()), int(lens.max()), default_scale(d),
+                                hkv, block_tables=bt.to(DEV))
+    torch.cuda.synchronize()
+    assert torch.isfinite(out.float()).all()
+    with_prefix = [i for i in range(128, 256) if int(prefix[i]) > 0]
+    sample = list(range(0, 128, 8)) + with_prefix[::max(1, len(with_prefix) // 16)][:16]
+    assert len(sample) >= 24
+    kch, vch = kc.cpu(), vc.cpu()
+    for i in sample:
+        a, b_ = int(cu_q[i]), int(cu_q[i + 1])
+        one_q = torch.tensor([0, b_ - a], dtype=torch.int32)
+        one_k = torch.tensor([0, int(lens[i])], dtype=torch.int32)
+        want = prefill_attn_ref(q[a:b_].cpu(), kch, vch, one_q, one_k, default_scale(d), bt[i:i + 1])
+        _close(out[a:b_], want)
+    _status_ok()
+
+
 def test_prefill_paged_block_size_512(b200):
     pkg, _ = b200
     g = torch.Generator().manual_seed(95)
@@ -523,4 +566,30 @@ def test_error_codes(b200):
     with pytest.raises(RuntimeError):
         pkg = b200[0]
         pkg.decode_attention(torch.zeros(1, 16, 128, dtype=torch.bfloat16), x, x, x, x, 0.1, 8)   # CPU tensor
+    _status_ok()
+
+
+def test_device_status_recovers_after_an_abandoned_launch(b200):
+    """The state a prefill launch leaves behind when one of its bounded waits gives up (status word set, ticket
+    counter never drawn to its end) is put in place from the host -- no kernel runs, nothing faults -- and
+    b200_device_status must report it once, repair it, and the next prefill must be complete and correct."""
+    from nanovllm_b200 import _lib
+    pkg, _ = b200
+    lib = _lib.load()
+    lens = [300, 64, 1, 700, 129]
+    q, k, v, cu_q, cu_k, _, fused = _prefill_case(77, lens, [0] * len(lens), 16, 8, paged=False)
+    want = prefill_attn_ref(q, k, v, cu_q, cu_k, default_scale(128))
+    kd = k.to(DEV)
+    vd = fused.to(DEV)[:, 8 * 128:].view(-1, 8, 128)
+    run = lambda: pkg.prefill_attention(q.to(DEV), kd, vd, cu_q.to(DEV), cu_k.to(DEV), max(lens), max(lens),
+                                        default_scale(128), 8)
+    _close(run(), want)
+    _status_ok()
+    assert lib.b200_test_inject_timeout() == 0
+    assert lib.b200_device_status() == -8
+    assert b"gave up" in lib.b200_last_error()
+    assert lib.b200_device_status() == 0          # reported once; the state is clean again
+    out = run()
+    torch.cuda.synchronize()
+    _close(out, want)                              # a stale ticket counter would have left rows unwritten
     _status_ok()

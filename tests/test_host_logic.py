@@ -8,7 +8,8 @@ import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 
-from oracle.attention_oracle import decode_attn_ref, default_scale, make_block_tables
+from oracle.attention_oracle import decode_attn_ref
+from workloads import default_scale, make_block_tables
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 REF = os.path.join(ROOT, "baseline", "_ref")
