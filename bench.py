@@ -198,13 +198,30 @@ class DecodeProblem:
         return o
 
 
-def time_steps(prob, ranks, steps, first):
-    """EXACTLY `steps` steps between barrier + synchronize on both sides; device time, max over ranks (ms)."""
+def capture_steps(prob, steps, first):
+    """The `steps` steps as one CUDA graph (the way the engine runs decode: nanovllm/engine/model_runner.py:215-250),
+    so that the timed region holds the kernels and not the host's launch calls."""
+    graph, side = torch.cuda.CUDAGraph(), torch.cuda.Stream()
+    torch.cuda.synchronize()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            for i in range(steps):
+                prob.step(first + i)
+    torch.cuda.synchronize()
+    return graph
+
+
+def time_steps(prob, ranks, steps, first, graph=None):
+    """EXACTLY `steps` steps between barrier + synchronize on both sides; device time, max over ranks (ms).
+    With `graph` (capture_steps of the same steps) the steps are one graph replay, else eager launches."""
     t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     ranks.barrier()
     t0.record()
-    for i in range(steps):
-        prob.step(first + i)
+    if graph is not None:
+        graph.replay()
+    else:
+        for i in range(steps):
+            prob.step(first + i)
     t1.record()
     ranks.barrier()
     return ranks.max(t0.elapsed_time(t1))
@@ -252,8 +269,16 @@ def run_decode(args, w, rank, world, local):
     ranks.barrier()
     # ---- timed region: K steps, inputs resident in HBM ----
     launches0 = lib.b200_launch_count()
-    ms_total = time_steps(prob, ranks, args.steps, args.warmup)
-    launches = lib.b200_launch_count() - launches0
+    graph = None if args.eager else capture_steps(prob, args.steps, args.warmup)    # 2 kernel nodes per step
+    if graph is not None:
+        time_steps(prob, ranks, args.steps, args.warmup, graph)                    # first replay: untimed
+        launches = lib.b200_launch_count() - launches0
+        ms_total = time_steps(prob, ranks, args.steps, args.warmup, graph)
+    else:
+        launches0 = lib.b200_launch_count()
+        ms_total = time_steps(prob, ranks, args.steps, args.warmup)
+        launches = lib.b200_launch_count() - launches0
+    eager_ms = time_steps(prob, ranks, args.steps, args.warmup) / args.steps
     dec_ms = time_decode_launches(prob, ranks, args.steps, args.warmup)
     # ---- end to end through the layer's forward, host buffers in, host result out ----
     for i in range(max(3, args.warmup)):
@@ -272,7 +297,7 @@ def run_decode(args, w, rank, world, local):
     skip = sampler.count() if rank == 0 else 0
     hold_ms, hold_steps, t_hold = [], 0, time.perf_counter()
     while True:
-        hold_ms.append(time_steps(prob, ranks, args.steps, 0) / args.steps)
+        hold_ms.append(time_steps(prob, ranks, args.steps, args.warmup, graph) / args.steps)
         hold_steps += args.steps
         flag = torch.tensor([1.0 if time.perf_counter() - t_hold < args.hold_seconds else 0.0], device=dev)
         if world > 1:
@@ -296,6 +321,7 @@ def run_decode(args, w, rank, world, local):
                    "sum_context": int(prob.lens.sum()), "block_size": BLOCK, "num_blocks": prob.nb,
                    "parallelism": f"tp{world} by kv head ({prob.hkv} kv heads per GPU), no collective",
                    "step": "store_kvcache(1 token/seq) + paged decode attention, one layer",
+                   "timed_region": "eager launches" if args.eager else "one CUDA graph of the K steps (2 kernel nodes per step)",
                    "l2": f"inputs larger than L2: steps rotate over {prob.layers} layer caches "
                          f"({prob.cache_gb():.2f} GB per GPU)",
                    "bytes_per_step_per_gpu": prob.step_bytes},
@@ -309,7 +335,7 @@ def run_decode(args, w, rank, world, local):
                 "h2d_bytes_per_step": int(sum(x.nbytes for x in (prob.hq, prob.hk, prob.hv, prob.h_slots, prob.h_lens, prob.h_bt))),
                 "d2h_bytes_per_step": int(prob.h_out.nbytes),
                 "api": "nanovllm_b200.Attention.forward with set_context, pinned host q/k/v/metadata in, host output out"},
-        "gpu_launches": int(launches),
+        "gpu_launches": int(launches), "eager_ms_per_step": round(eager_ms, 5),
         "hold": {"seconds": args.hold_seconds, "steps": hold_steps, "ms_per_step": round(hold_med, 5),
                  "value": round(world * prob.step_bytes / (hold_med * 1e-3) / 1e9, 1)},
         "clocks": clocks,
@@ -341,7 +367,10 @@ def secondary_decode(args, name, rank, world, dev, ranks, steps=30):
     prob = DecodeProblem(w, rank, world, dev, w["layers"])
     for i in range(3):
         prob.step(i)
-    ms = time_steps(prob, ranks, steps, 3) / steps
+    graph = None if args.eager else capture_steps(prob, steps, 3)
+    if graph is not None:
+        time_steps(prob, ranks, steps, 3, graph)
+    ms = time_steps(prob, ranks, steps, 3, graph) / steps
     dec_ms = time_decode_launches(prob, ranks, steps, 3)
     pk = peaks()
     per_gpu = prob.step_bytes / (ms * 1e-3) / 1e9
@@ -637,6 +666,7 @@ def main():
     ap.add_argument("--no-secondary", action="store_true", help="skip the library baseline and the secondary workloads")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--layers", type=int, default=0, help="layer caches the steps rotate over (0 = workload default)")
+    ap.add_argument("--eager", action="store_true", help="time eager launches instead of one CUDA graph of the K steps")
     ap.add_argument("--hold-seconds", type=float, default=2.0,
                     help="how long the steps are repeated after the timed region for the clock samples")
     args = ap.parse_args()

@@ -211,10 +211,13 @@ decode_attn_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap map
     mbar_fence_init();
   }
 
-  // Launched with programmatic stream serialization: everything above overlapped the tail of
-  // the previous kernel in the stream (store_kvcache); nothing below may run before that kernel
-  // has finished and its writes are visible.
-  asm volatile("griddepcontrol.wait;" ::: "memory");
+  // Launched with programmatic stream serialization: the kernel may start while the previous kernel
+  // of the stream is still running, if that kernel allows it (griddepcontrol.launch_dependents; only
+  // this library's store and producer kernels do, any other kernel has completed before this one
+  // starts).  Those kernels write K/V rows of the cache and the query rows, never the metadata, so
+  // the scan over context_lens, the piece geometry and the first block-table reads below run ahead;
+  // every thread that goes on to touch q, the cache, the output or the workspace first executes
+  // griddepcontrol.wait (the consumer warps only ever read shared memory filled after it).
 
   // ---- tile counts per sequence and their exclusive prefix (block scan) ----
   {
@@ -256,11 +259,14 @@ decode_attn_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap map
     __syncthreads();
   }
 
-  // ---- sequences with no context produce zeros ----
-  for (int i = blockIdx.x; i < p.batch; i += gridDim.x) {
-    if (s_prefix[i + 1] == s_prefix[i]) {
-      uint4* o = reinterpret_cast<uint4*>(p.out + static_cast<long long>(i) * p.H * 128);
-      for (int v = tid; v < p.H * 16; v += kDecThreads) o[v] = make_uint4(0, 0, 0, 0);
+  // ---- sequences with no context produce zeros (the epilogue warp's job, before anything else) ----
+  if (warp == kDecEpilogueWarp) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    for (int i = blockIdx.x; i < p.batch; i += gridDim.x) {
+      if (s_prefix[i + 1] == s_prefix[i]) {
+        uint4* o = reinterpret_cast<uint4*>(p.out + static_cast<long long>(i) * p.H * 128);
+        for (int v = lane; v < p.H * 16; v += 32) o[v] = make_uint4(0, 0, 0, 0);
+      }
     }
   }
 
@@ -290,6 +296,7 @@ decode_attn_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap map
     int cur_col0 = (cur.t0 * kTile) / p.block_size;
     int cur_blk0 = cur_bt[cur_col0];
     int cur_blk1 = cur_col0 + 1 < p.bt_cols ? cur_bt[cur_col0 + 1] : -1;
+    asm volatile("griddepcontrol.wait;" ::: "memory");   // from here on: query rows and the cache
     while (true) {
       cur_len = cur_len > max_len ? max_len : cur_len;
       cur.len = cur_len;
@@ -425,70 +432,116 @@ decode_attn_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap map
         const SegDesc d = s_pending[k];
         const int i_first = pc.of(d.seg_start);
         const int n = pc.of(d.seg_start + d.nt - 1) - i_first + 1;
-        for (int gq = 0; gq < G; ++gq) {
-          float M = -INFINITY, L = 0.f;
-          float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-          for (int base = 0; base < n; base += 32) {
-            const int cnt = n - base < 32 ? n - base : 32;
-            // lane j looks after partial base + j: its slot, its (max, sum)
-            int sl = 0;
-            float mj = -INFINITY, lj = 0.f;
-            if (lane < cnt) {
-              const int i = i_first + base + lane;
-              sl = i * 2 + (d.seg_start <= pc.start(i) ? 0 : 1);
-              const float2 v = __ldcg(reinterpret_cast<const float2*>(p.ws_ml + (sl * G + gq) * 2));
-              mj = v.x;
-              lj = v.y;
-            }
-            float Mr = mj;
+        if (n <= 4) {
+          // The common case (a few partials): all loads of a query head are issued before the first is used,
+          // one trip to L2 per head instead of two.
+          int sl[4];
 #pragma unroll
-            for (int off = 16; off > 0; off >>= 1) Mr = fmaxf(Mr, __shfl_xor_sync(0xffffffffu, Mr, off));
-            const float Mn = fmaxf(M, Mr);
-            const float rescale = fast_exp2(M - Mn);
-            const float wj = fast_exp2(mj - Mn);
-            float Lr = lj * wj;
-#pragma unroll
-            for (int off = 16; off > 0; off >>= 1) Lr += __shfl_xor_sync(0xffffffffu, Lr, off);
-            L = L * rescale + Lr;
-            acc.x *= rescale; acc.y *= rescale; acc.z *= rescale; acc.w *= rescale;
-            M = Mn;
-            // every lane accumulates its 4 dims over the partials, 8 independent loads at a time
-            for (int u0 = 0; u0 < cnt; u0 += 8) {
-              float4 v[8];
-#pragma unroll
-              for (int u = 0; u < 8; ++u) {
-                const int slu = __shfl_sync(0xffffffffu, sl, (u0 + u) & 31);
-                if (u0 + u < cnt)
-                  v[u] = __ldcg(reinterpret_cast<const float4*>(p.ws_o + (static_cast<long long>(slu) * G + gq) * 128 + lane * 4));
-              }
-#pragma unroll
-              for (int u = 0; u < 8; ++u) {
-                const float wu = __shfl_sync(0xffffffffu, wj, (u0 + u) & 31);
-                if (u0 + u < cnt) { acc.x += v[u].x * wu; acc.y += v[u].y * wu; acc.z += v[u].z * wu; acc.w += v[u].w * wu; }
-              }
-            }
+          for (int u = 0; u < 4; ++u) {
+            const int i = i_first + (u < n ? u : 0);
+            sl[u] = i * 2 + (d.seg_start <= pc.start(i) ? 0 : 1);
           }
-          const float inv = 1.f / L;
-          uint2 o2;
-          o2.x = pack_bf16(acc.x * inv, acc.y * inv);
-          o2.y = pack_bf16(acc.z * inv, acc.w * inv);
-          *reinterpret_cast<uint2*>(p.out + (static_cast<long long>(d.seq) * p.H + d.h * G + gq) * 128 + lane * 4) = o2;
+#pragma unroll 1
+          for (int gq = 0; gq < G; ++gq) {
+            float4 v[4];
+            float2 ml[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              if (u < n) {
+                v[u] = __ldcg(reinterpret_cast<const float4*>(p.ws_o + (static_cast<long long>(sl[u]) * G + gq) * 128 + lane * 4));
+                ml[u] = __ldcg(reinterpret_cast<const float2*>(p.ws_ml + (sl[u] * G + gq) * 2));
+              }
+            }
+            float M = -INFINITY;
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+              if (u < n) M = fmaxf(M, ml[u].x);
+            float L = 0.f;
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              if (u < n) {
+                const float wu = fast_exp2(ml[u].x - M);
+                L += ml[u].y * wu;
+                acc.x += v[u].x * wu; acc.y += v[u].y * wu; acc.z += v[u].z * wu; acc.w += v[u].w * wu;
+              }
+            }
+            const float inv = 1.f / L;
+            uint2 o2;
+            o2.x = pack_bf16(acc.x * inv, acc.y * inv);
+            o2.y = pack_bf16(acc.z * inv, acc.w * inv);
+            *reinterpret_cast<uint2*>(p.out + (static_cast<long long>(d.seq) * p.H + d.h * G + gq) * 128 + lane * 4) = o2;
+          }
+        } else {
+          for (int gq = 0; gq < G; ++gq) {
+            float M = -INFINITY, L = 0.f;
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int base = 0; base < n; base += 32) {
+              const int cnt = n - base < 32 ? n - base : 32;
+              // lane j looks after partial base + j: its slot, its (max, sum)
+              int sl = 0;
+              float mj = -INFINITY, lj = 0.f;
+              if (lane < cnt) {
+                const int i = i_first + base + lane;
+                sl = i * 2 + (d.seg_start <= pc.start(i) ? 0 : 1);
+                const float2 v = __ldcg(reinterpret_cast<const float2*>(p.ws_ml + (sl * G + gq) * 2));
+                mj = v.x;
+                lj = v.y;
+              }
+              float Mr = mj;
+  #pragma unroll
+              for (int off = 16; off > 0; off >>= 1) Mr = fmaxf(Mr, __shfl_xor_sync(0xffffffffu, Mr, off));
+              const float Mn = fmaxf(M, Mr);
+              const float rescale = fast_exp2(M - Mn);
+              const float wj = fast_exp2(mj - Mn);
+              float Lr = lj * wj;
+  #pragma unroll
+              for (int off = 16; off > 0; off >>= 1) Lr += __shfl_xor_sync(0xffffffffu, Lr, off);
+              L = L * rescale + Lr;
+              acc.x *= rescale; acc.y *= rescale; acc.z *= rescale; acc.w *= rescale;
+              M = Mn;
+              // every lane accumulates its 4 dims over the partials, 8 independent loads at a time
+              for (int u0 = 0; u0 < cnt; u0 += 8) {
+                float4 v[8];
+  #pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                  const int slu = __shfl_sync(0xffffffffu, sl, (u0 + u) & 31);
+                  if (u0 + u < cnt)
+                    v[u] = __ldcg(reinterpret_cast<const float4*>(p.ws_o + (static_cast<long long>(slu) * G + gq) * 128 + lane * 4));
+                }
+  #pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                  const float wu = __shfl_sync(0xffffffffu, wj, (u0 + u) & 31);
+                  if (u0 + u < cnt) { acc.x += v[u].x * wu; acc.y += v[u].y * wu; acc.z += v[u].z * wu; acc.w += v[u].w * wu; }
+                }
+              }
+            }
+            const float inv = 1.f / L;
+            uint2 o2;
+            o2.x = pack_bf16(acc.x * inv, acc.y * inv);
+            o2.y = pack_bf16(acc.z * inv, acc.w * inv);
+            *reinterpret_cast<uint2*>(p.out + (static_cast<long long>(d.seq) * p.H + d.h * G + gq) * 128 + lane * 4) = o2;
+          }
         }
         if (lane == 0) p.counters[d.seq * Hkv + d.h] = 0;
       }
       __syncwarp();
       n_pending = 0;
     };
-    bool ok = true;
-    for (int n = 0;; ++n) {
+    // (flush() is expanded in one place only: it is large, and three copies cost the kernel registers)
+    bool finished = false, flush_now = false;
+    for (int n = 0;;) {
       const int e = n % p.n_merge;
       const uint32_t ph = (n / p.n_merge) & 1;
-      if (!mbar_try_wait(&bar_merge_full[e], ph)) {
-        flush();                                   // nothing to combine right now: do the slow part
-        if (!mbar_wait(&bar_merge_full[e], ph, abort_flag)) { ok = false; break; }
+      const bool ready = !finished && !flush_now && mbar_try_wait(&bar_merge_full[e], ph);
+      flush_now = false;
+      if (!ready) {
+        flush();                                     // nothing to combine right now: do the slow part
+        if (finished) break;
+        if (!mbar_wait(&bar_merge_full[e], ph, abort_flag)) break;
       }
       const SegDesc d = s_merge_desc[e];
-      if (d.seq < 0) break;
+      if (d.seq < 0) { finished = true; continue; }
       const float* mo = merge_o + e * kDecConsumerWarps * G * 128;
       const float* ml = merge_ml + e * kDecConsumerWarps * G * 2;
       const bool full = d.t0 == 0 && d.t1 == d.nt;
@@ -518,13 +571,13 @@ decode_attn_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap map
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(&bar_merge_empty[e]);   // the consumers may refill the hand-off buffer
+      ++n;
       if (!full) {
         if (lane == 0) s_pending[n_pending] = d;
         __syncwarp();
-        if (++n_pending == kDecPending) flush();
+        if (++n_pending == kDecPending) flush_now = true;   // a full queue is flushed at the top of the loop
       }
     }
-    if (ok) flush();
     if (lane == 0) DEC_TRACE(4);
     return;
   }
