@@ -152,6 +152,21 @@ int b200_qk_norm_rope_store(const void* qkv, int64_t qkv_row_stride, const int64
                             int64_t n_slots, int32_t n_tokens, int32_t num_heads, int32_t num_kv_heads,
                             int32_t head_dim, void* stream);
 
+/* ---- caller side of the decode path: a step's metadata into the graph's static buffers in one launch -----
+ * Replaces, for one decode step, the seven device operations with which the reference's model runner moves
+ * its freshly copied metadata into the buffers its CUDA graphs were captured on
+ * (nanovllm/engine/model_runner.py:193-203), and lets its five host-to-device copies (:163-179, :119-123)
+ * become one: the host packs the step into one record,
+ *   int64 input_ids[batch] | int64 positions[batch] | int32 slot_mapping[batch] | int32 context_lens[batch] |
+ *   int32 block_tables[batch][table_width]  (rows padded with -1)
+ * copies it to the device (8-byte aligned), and this call scatters it with the reference's exact effect:
+ * rows [0, batch) of input_ids and positions are written; slot_mapping is -1 and context_lens 0 on rows
+ * [batch, buffer_rows); block_tables (row stride buffer_table_cols) gets columns [0, table_width) of rows
+ * [0, batch) and keeps the rest.  batch <= buffer_rows and table_width <= buffer_table_cols. */
+int b200_unpack_decode_metadata(const void* packed, int32_t batch, int32_t table_width, int32_t buffer_rows,
+                                int32_t buffer_table_cols, int64_t* input_ids, int64_t* positions,
+                                int32_t* slot_mapping, int32_t* context_lens, int32_t* block_tables, void* stream);
+
 /* Number of kernels this library has launched from the calling process so far (all threads).
  * Benchmarks use the difference across a timed region. */
 int64_t b200_launch_count(void);

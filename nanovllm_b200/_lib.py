@@ -34,6 +34,8 @@ SIGNATURES = {
     "b200_qk_norm_rope_store": (c_int32, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_float,
                                           c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int32, c_int32,
                                           c_int32, c_int32, c_void_p]),
+    "b200_unpack_decode_metadata": (c_int32, [c_void_p, c_int32, c_int32, c_int32, c_int32, c_void_p, c_void_p, c_void_p,
+                                              c_void_p, c_void_p, c_void_p]),
     "b200_launch_count": (c_int64, []),
     "b200_device_status": (c_int32, []),
     "b200_test_inject_timeout": (c_int32, []),

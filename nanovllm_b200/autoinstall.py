@@ -7,6 +7,8 @@ this module in every process closes that gap:
     B200_ATTN_INSTALL=1        install the attention layer
     B200_ATTN_INSTALL=fused    also replace Qwen3Attention.forward by the fused producer
                                (QK-norm + RoPE + cache store in one kernel)
+    B200_ATTN_INSTALL=full     also rebind the model runner's decode metadata preparation
+                               (one packed host-to-device copy and one launch per step)
 
 Two ways to get it imported in the children: import it at the top of the script that creates the `LLM`
 (spawn re-imports that script's module in every child), or put a one-line `.pth` file into site-packages,
@@ -21,5 +23,5 @@ _mode = os.environ.get("B200_ATTN_INSTALL", "")
 installed = False
 if _mode and _mode != "0":
     from . import integration as _integration
-    _integration.install(fuse_qk_norm_rope=(_mode == "fused"))
+    _integration.install(fuse_qk_norm_rope=_mode in ("fused", "full"), fast_decode_metadata=(_mode == "full"))
     installed = True

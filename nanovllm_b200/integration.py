@@ -18,10 +18,13 @@ import importlib
 import sys
 
 
-def install(fuse_qk_norm_rope: bool = False):
+def install(fuse_qk_norm_rope: bool = False, fast_decode_metadata: bool = False):
     """fuse_qk_norm_rope=True additionally replaces the body of `Qwen3Attention.forward`
     (nanovllm/models/qwen3.py:68-82) by one that runs q_norm, k_norm, rotary_emb and the cache store as a
-    single kernel (layers/qk_norm_rope.py); nano-vllm's model module is imported for that."""
+    single kernel (layers/qk_norm_rope.py); nano-vllm's model module is imported for that.
+    fast_decode_metadata=True rebinds `ModelRunner.prepare_decode` and the graph branch of `ModelRunner.run_model`
+    (nanovllm/engine/model_runner.py:163-179, :188-205) to the packed one-copy, one-launch form of
+    engine/decode_metadata.py."""
     from .layers import attention as ours
     ref_attn = sys.modules.get("nanovllm.layers.attention")
     if ref_attn is None:
@@ -43,4 +46,8 @@ def install(fuse_qk_norm_rope: bool = False):
         from .layers.qk_norm_rope import fused_attention_forward
         qwen3 = importlib.import_module("nanovllm.models.qwen3")
         qwen3.Qwen3Attention.forward = fused_attention_forward
+    if fast_decode_metadata:
+        from .engine.decode_metadata import install_into
+        runner = importlib.import_module("nanovllm.engine.model_runner")
+        install_into(runner.ModelRunner, ref_ctx)
     return ours
