@@ -5,7 +5,8 @@
 //   store_kvcache        nanovllm/layers/attention.py:10-40    (called at layers/attention.py:62-63)
 // which the reference runs as three compiled element-wise kernels plus one Triton kernel.
 //
-// A half-warp owns one 128-element head vector of one token: lane j of 16 holds elements [8j, 8j + 8)
+// A half-warp owns one 128-element head vector at a time (four consecutive heads of a token per pass):
+// lane j of 16 holds elements [8j, 8j + 8)
 // (16-byte accesses), so the rotary partner (element i +- 64) of every element sits in lane j ^ 8.  q heads and k heads are
 // normalised in fp32, cast to bf16, multiplied by the bf16 weight, rotated in fp32 (products and
 // sums rounded separately, as the reference's eager arithmetic does) and written out contiguous;
@@ -39,107 +40,152 @@ struct QkNormRopeParams {
   int n_tokens, H, Hkv;
 };
 
-constexpr int kQkThreads = 256;     // 16 head vectors per CTA pass: one per half-warp
+constexpr int kQkThreads = 256;     // 16 half-warps per CTA
+constexpr int kQkGroup = 4;         // head vectors of one token a half-warp works through per pass (large batches)
 
-__device__ __forceinline__ void bf16x8_to_float(const uint4& r, float (&x)[8]) {
-  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&r);
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    x[2 * i] = __low2float(h[i]);
-    x[2 * i + 1] = __high2float(h[i]);
-  }
+__device__ __forceinline__ unsigned long long f32x2_mul(unsigned long long a, unsigned long long b) {
+  unsigned long long d;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
 }
 
-// One head vector: `raw` holds this lane's 8 elements of head `hd` of token `tok`.
-__device__ __forceinline__ void qk_one_vector(const QkNormRopeParams& p, int tok, int hd, const uint4& raw, int sub,
-                                              unsigned half_mask) {
-  long long slot = -1;
+// bf16 pair -> packed fp32 pair (exact)
+__device__ __forceinline__ unsigned long long bf16x2_to_f32x2(uint32_t v) {
+  return f32x2_pack(__uint_as_float(v << 16), __uint_as_float(v & 0xffff0000u));
+}
+
+// What a half-warp needs once per token (not once per head): where the token goes in the cache and this
+// lane's eight cos / sin values of its position.
+struct QkTokenCtx {
+  long long slot;                      // -1: no store
+  unsigned long long cosv[4], sinv[4]; // packed pairs; sin carries the sign of this lane's half (-sin for the first)
+};
+
+__device__ __forceinline__ QkTokenCtx qk_token_ctx(const QkNormRopeParams& p, int tok, int sub) {
+  QkTokenCtx c;
+  c.slot = -1;
   if (p.slot_mapping && p.k_cache && p.v_cache) {
-    slot = p.slot_mapping[tok];
-    if (slot >= p.n_slots) slot = -1;                    // never write outside the cache
+    c.slot = p.slot_mapping[tok];
+    if (c.slot >= p.n_slots) c.slot = -1;                // never write outside the cache
   }
-  if (hd >= p.H + p.Hkv) {
-    // v head: a bit copy into the cache
-    if (slot >= 0)
-      *reinterpret_cast<uint4*>(p.v_cache + (slot * p.Hkv + (hd - p.H - p.Hkv)) * 128 + sub * 8) = raw;
-    return;
-  }
-  const bool is_q = hd < p.H;
   long long pos = p.positions[tok];
   pos = pos < 0 ? 0 : (pos >= p.max_position ? p.max_position - 1 : pos);
   const float* cs = p.cos_sin + pos * 128 + (sub & 7) * 8;
   const float4 c0 = *reinterpret_cast<const float4*>(cs), c1 = *reinterpret_cast<const float4*>(cs + 4);
   const float4 s0 = *reinterpret_cast<const float4*>(cs + 64), s1 = *reinterpret_cast<const float4*>(cs + 68);
-  const uint4 wraw = *reinterpret_cast<const uint4*>((is_q ? p.q_weight : p.k_weight) + sub * 8);
-  float x[8], w[8];
-  bf16x8_to_float(raw, x);
-  bf16x8_to_float(wraw, w);
+  // first half:  y1 = x1 * cos - x2 * sin      second half:  y2 = x2 * cos + x1 * sin
+  // (negating sin is exact, and a + (-t) rounds like a - t)
+  const float sg = sub < 8 ? -1.f : 1.f;
+  c.cosv[0] = f32x2_pack(c0.x, c0.y); c.cosv[1] = f32x2_pack(c0.z, c0.w);
+  c.cosv[2] = f32x2_pack(c1.x, c1.y); c.cosv[3] = f32x2_pack(c1.z, c1.w);
+  c.sinv[0] = f32x2_pack(sg * s0.x, sg * s0.y); c.sinv[1] = f32x2_pack(sg * s0.z, sg * s0.w);
+  c.sinv[2] = f32x2_pack(sg * s1.x, sg * s1.y); c.sinv[3] = f32x2_pack(sg * s1.z, sg * s1.w);
+  return c;
+}
+
+// One q or k head vector: `raw` holds this lane's 8 elements; `w` the lane's 8 weights as packed fp32 pairs.
+// Every product and every sum is rounded on its own (mul.rn / add.rn, packed two at a time), in the order the
+// reference's eager arithmetic takes them.
+__device__ __forceinline__ uint4 qk_norm_rope_vector(const uint4& raw, const unsigned long long (&w)[4],
+                                                     const QkTokenCtx& c, float eps, unsigned half_mask) {
+  const uint32_t r[4] = {raw.x, raw.y, raw.z, raw.w};
+  unsigned long long x[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) x[i] = bf16x2_to_f32x2(r[i]);
   // mean of squares over the 128 elements, fp32
   float ss = 0.f;
 #pragma unroll
-  for (int i = 0; i < 8; ++i) ss = __fadd_rn(ss, __fmul_rn(x[i], x[i]));
+  for (int i = 0; i < 4; ++i) {
+    float q0, q1;
+    f32x2_unpack(f32x2_mul(x[i], x[i]), q0, q1);
+    ss = __fadd_rn(__fadd_rn(ss, q0), q1);
+  }
 #pragma unroll
   for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(half_mask, ss, o);
-  const float rinv = __frsqrt_rn(__fadd_rn(__fdiv_rn(ss, 128.f), p.eps));
-  const float cosv[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
-  const float sinv[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+  const float rinv = __frsqrt_rn(__fadd_rn(__fdiv_rn(ss, 128.f), eps));
+  const unsigned long long rinv2 = f32x2_pack(rinv, rinv);
   // normalise in fp32, round to bf16, scale by the bf16 weight (rounded to bf16 again); the results are
   // exact bf16 values, so they travel to the partner lane as packed pairs (4 shuffles instead of 8)
   uint32_t ap[4];
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    const __nv_bfloat162 n2 = __floats2bfloat162_rn(__fmul_rn(x[2 * i], rinv), __fmul_rn(x[2 * i + 1], rinv));
-    ap[i] = pack_bf16(__fmul_rn(__low2float(n2), w[2 * i]), __fmul_rn(__high2float(n2), w[2 * i + 1]));
+    float n0, n1, m0, m1;
+    f32x2_unpack(f32x2_mul(x[i], rinv2), n0, n1);
+    f32x2_unpack(f32x2_mul(bf16x2_to_f32x2(pack_bf16(n0, n1)), w[i]), m0, m1);
+    ap[i] = pack_bf16(m0, m1);
   }
-  float y[8];
+  uint32_t y[4];
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     const uint32_t bp = __shfl_xor_sync(half_mask, ap[i], 8);       // the elements 64 away
-    const __nv_bfloat162 a2 = *reinterpret_cast<const __nv_bfloat162*>(&ap[i]);
-    const __nv_bfloat162 b2 = *reinterpret_cast<const __nv_bfloat162*>(&bp);
-    const float a0 = __low2float(a2), a1 = __high2float(a2), b0 = __low2float(b2), b1 = __high2float(b2);
-    // first half:  y1 = x1 * cos - x2 * sin      second half:  y2 = x2 * cos + x1 * sin
-    const float t0 = __fmul_rn(b0, sinv[2 * i]), t1 = __fmul_rn(b1, sinv[2 * i + 1]);
-    y[2 * i] = __fadd_rn(__fmul_rn(a0, cosv[2 * i]), sub < 8 ? -t0 : t0);
-    y[2 * i + 1] = __fadd_rn(__fmul_rn(a1, cosv[2 * i + 1]), sub < 8 ? -t1 : t1);
+    float y0, y1;
+    f32x2_unpack(f32x2_add(f32x2_mul(bf16x2_to_f32x2(ap[i]), c.cosv[i]), f32x2_mul(bf16x2_to_f32x2(bp), c.sinv[i])), y0, y1);
+    y[i] = pack_bf16(y0, y1);
   }
-  uint4 outw;
-  outw.x = pack_bf16(y[0], y[1]);
-  outw.y = pack_bf16(y[2], y[3]);
-  outw.z = pack_bf16(y[4], y[5]);
-  outw.w = pack_bf16(y[6], y[7]);
-  if (is_q) {
-    *reinterpret_cast<uint4*>(p.q_out + (static_cast<long long>(tok) * p.H + hd) * 128 + sub * 8) = outw;
-  } else {
-    const int kh = hd - p.H;
-    *reinterpret_cast<uint4*>(p.k_out + (static_cast<long long>(tok) * p.Hkv + kh) * 128 + sub * 8) = outw;
-    if (slot >= 0) *reinterpret_cast<uint4*>(p.k_cache + (slot * p.Hkv + kh) * 128 + sub * 8) = outw;
-  }
+  return make_uint4(y[0], y[1], y[2], y[3]);
 }
 
-__global__ void __launch_bounds__(kQkThreads, 4)
+__device__ __forceinline__ void qk_weight_pairs(const __nv_bfloat16* wt, int sub, unsigned long long (&w)[4]) {
+  const uint4 wraw = *reinterpret_cast<const uint4*>(wt + sub * 8);
+  w[0] = bf16x2_to_f32x2(wraw.x); w[1] = bf16x2_to_f32x2(wraw.y);
+  w[2] = bf16x2_to_f32x2(wraw.z); w[3] = bf16x2_to_f32x2(wraw.w);
+}
+
+template <int GROUP>
+__global__ void __launch_bounds__(kQkThreads, GROUP == 1 ? 4 : 3)
 qk_norm_rope_store_kernel(const QkNormRopeParams p) {
-  // a half-warp owns one head vector: lane j of 16 holds elements [8j, 8j + 8) (one 16-byte access),
-  // the rotary partner (element i +- 64) of each of them sits in lane j ^ 8; two vectors are in flight
-  // per half-warp so that the second load is on its way while the first is worked on
+  // A half-warp owns one head vector at a time: lane j of 16 holds elements [8j, 8j + 8) (one 16-byte access),
+  // the rotary partner (element i +- 64) of each of them sits in lane j ^ 8.  It takes GROUP consecutive
+  // heads of one token per pass -- all loads of the pass go out first -- so that what belongs to the token
+  // (slot, position, the lane's cos / sin values) and to the head kind (the norm weight) is fetched once per
+  // pass instead of once per head.  GROUP = 1 for decode-sized batches, where the launch is latency bound
+  // and more half-warps in flight matter more than the instructions saved.
   const int sub = threadIdx.x & 15;
   const int heads = p.H + 2 * p.Hkv;
-  const long long n_vec = static_cast<long long>(p.n_tokens) * heads;
+  const int groups = (heads + GROUP - 1) / GROUP;                       // per token
+  const long long n_units = static_cast<long long>(p.n_tokens) * groups;
   const long long stride = static_cast<long long>(gridDim.x) * (kQkThreads / 16);
   const unsigned half_mask = 0xffffu << (threadIdx.x & 16);
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  for (long long vec = static_cast<long long>(blockIdx.x) * (kQkThreads / 16) + (threadIdx.x >> 4); vec < n_vec;
-       vec += 2 * stride) {
-    const long long vec2 = vec + stride;
-    const int tok = static_cast<int>(vec / heads);
-    const int hd = static_cast<int>(vec - static_cast<long long>(tok) * heads);
-    const bool two = vec2 < n_vec;
-    const int tok2 = two ? static_cast<int>(vec2 / heads) : tok;
-    const int hd2 = two ? static_cast<int>(vec2 - static_cast<long long>(tok2) * heads) : hd;
-    const uint4 raw = *reinterpret_cast<const uint4*>(p.qkv + tok * p.qkv_row_stride + hd * 128 + sub * 8);
-    const uint4 raw2 = *reinterpret_cast<const uint4*>(p.qkv + tok2 * p.qkv_row_stride + hd2 * 128 + sub * 8);
-    qk_one_vector(p, tok, hd, raw, sub, half_mask);
-    if (two) qk_one_vector(p, tok2, hd2, raw2, sub, half_mask);
+  unsigned long long wq[4], wk[4];
+  if (GROUP > 1) {
+    qk_weight_pairs(p.q_weight, sub, wq);
+    qk_weight_pairs(p.k_weight, sub, wk);
+  }
+  for (long long unit = static_cast<long long>(blockIdx.x) * (kQkThreads / 16) + (threadIdx.x >> 4); unit < n_units;
+       unit += stride) {
+    const int tok = static_cast<int>(unit / groups);
+    const int hd0 = static_cast<int>(unit - static_cast<long long>(tok) * groups) * GROUP;
+    const __nv_bfloat16* row = p.qkv + tok * p.qkv_row_stride + sub * 8;
+    uint4 raw[GROUP];
+#pragma unroll
+    for (int g = 0; g < GROUP; ++g)
+      if (hd0 + g < heads) raw[g] = *reinterpret_cast<const uint4*>(row + (hd0 + g) * 128);
+    if (GROUP == 1 && hd0 < p.H + p.Hkv) {
+      // one head per pass: only the weight of its kind (both sets would cost registers the pass does not have)
+      qk_weight_pairs(hd0 < p.H ? p.q_weight : p.k_weight, sub, wq);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) wk[i] = wq[i];
+    }
+    const QkTokenCtx c = qk_token_ctx(p, tok, sub);
+#pragma unroll
+    for (int g = 0; g < GROUP; ++g) {
+      const int hd = hd0 + g;
+      if (hd >= heads) break;
+      if (hd >= p.H + p.Hkv) {
+        // v head: a bit copy into the cache
+        if (c.slot >= 0)
+          *reinterpret_cast<uint4*>(p.v_cache + (c.slot * p.Hkv + (hd - p.H - p.Hkv)) * 128 + sub * 8) = raw[g];
+      } else if (hd < p.H) {
+        const uint4 outw = qk_norm_rope_vector(raw[g], wq, c, p.eps, half_mask);
+        *reinterpret_cast<uint4*>(p.q_out + (static_cast<long long>(tok) * p.H + hd) * 128 + sub * 8) = outw;
+      } else {
+        const int kh = hd - p.H;
+        const uint4 outw = qk_norm_rope_vector(raw[g], wk, c, p.eps, half_mask);
+        *reinterpret_cast<uint4*>(p.k_out + (static_cast<long long>(tok) * p.Hkv + kh) * 128 + sub * 8) = outw;
+        if (c.slot >= 0) *reinterpret_cast<uint4*>(p.k_cache + (c.slot * p.Hkv + kh) * 128 + sub * 8) = outw;
+      }
+    }
   }
 }
 
@@ -186,12 +232,20 @@ extern "C" int b200_qk_norm_rope_store(const void* qkv, int64_t qkv_row_stride, 
   p.n_tokens = n_tokens;
   p.H = num_heads;
   p.Hkv = num_kv_heads;
-  const long long n_vec = static_cast<long long>(n_tokens) * (num_heads + 2 * num_kv_heads);
   const int sms = sm_count();
   if (sms <= 0) return set_error(kErrNoDriver, "qk_norm_rope_store: no CUDA device");
-  const long long want = (n_vec + kQkThreads / 16 - 1) / (kQkThreads / 16);
-  const int grid = static_cast<int>(want < static_cast<long long>(sms) * 8 ? want : static_cast<long long>(sms) * 8);
-  qk_norm_rope_store_kernel<<<grid, kQkThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  const int heads = num_heads + 2 * num_kv_heads;
+  // one head per pass while that still leaves fewer half-warps than the device can hold
+  const bool small = static_cast<long long>(n_tokens) * heads <= static_cast<long long>(sms) * 6 * (kQkThreads / 16);
+  const int group = small ? 1 : kQkGroup;
+  const long long n_units = static_cast<long long>(n_tokens) * ((heads + group - 1) / group);
+  const long long want = (n_units + kQkThreads / 16 - 1) / (kQkThreads / 16);
+  const long long cap = static_cast<long long>(sms) * (small ? 8 : 6);
+  const int grid = static_cast<int>(want < cap ? want : cap);
+  if (small)
+    qk_norm_rope_store_kernel<1><<<grid, kQkThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  else
+    qk_norm_rope_store_kernel<kQkGroup><<<grid, kQkThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
   g_launches.fetch_add(1);
   return check_cuda(cudaGetLastError(), "qk_norm_rope_store launch");
 }
