@@ -88,7 +88,7 @@ int b200_decode_attn(const void* q, int64_t q_row_stride, const void* k_cache, c
  * fail), a plugin interface that forbids allocating inside the call, code that must stay away from
  * the framework's allocator.  This variant computes exactly what b200_decode_attn computes, with
  * the same arguments minus the workspace, and keeps its scratch inside the library: a __device__
- * array of b200_decode_static_scratch_bytes() (about 8.4 MiB) that every GPU which loads the
+ * array of b200_decode_static_scratch_bytes() (8 249 600 bytes, about 7.9 MiB) that every GPU which loads the
  * library holds until the process exits.  It calls no cudaMalloc/cudaFree and no allocating
  * library routine.
  *
