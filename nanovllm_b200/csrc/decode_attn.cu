@@ -72,18 +72,6 @@ struct DecodeParams {
   unsigned int* ticket;  // piece scheduler, zero between launches
 };
 
-// Optional per-CTA timestamps (compile with -DB200_TRACE; read with b200_debug_trace).  Off by default.
-#ifdef B200_TRACE
-__device__ unsigned long long g_dec_trace[1024 * 8];
-__device__ __forceinline__ unsigned long long trace_now() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
-#define DEC_TRACE(slot) do { g_dec_trace[blockIdx.x * 8 + (slot)] = trace_now(); } while (0)
-#else
-#define DEC_TRACE(slot) do { } while (0)
-#endif
 
 // One (sequence, kv head) segment inside one piece, as the producer hands it to the other warps.
 struct SegDesc {
@@ -196,7 +184,6 @@ decode_attn_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap map
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int max_len = p.bt_cols * p.block_size;
-  if (tid == 0) DEC_TRACE(0);
 
   if (tid == 0) {
     s_abort = 0;
@@ -274,7 +261,6 @@ decode_attn_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap map
   const DecPieces pc = dec_pieces(T, static_cast<int>(gridDim.x), p.dyn_factor, p.big_pct, p.small_pct100, p.small_n);
   const int cta = blockIdx.x;
   if (cta >= pc.g) return;
-  if (tid == 0) DEC_TRACE(1);
 
   volatile int* abort_flag = &s_abort;
 
@@ -578,7 +564,6 @@ decode_attn_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap map
         if (++n_pending == kDecPending) flush_now = true;   // a full queue is flushed at the top of the loop
       }
     }
-    if (lane == 0) DEC_TRACE(4);
     return;
   }
 
@@ -597,7 +582,6 @@ decode_attn_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap map
     }
     const SegDesc d = s_desc[segc % kSegRing];
     if (d.seq < 0) break;
-    if (tid == 0 && it == 0) DEC_TRACE(2);
     uint32_t qa[8][4];   // query fragments: rows = the G heads sharing the kv head
     {
       const uint32_t* q0 = reinterpret_cast<const uint32_t*>(s_q + (segc % kSegRing) * G * 128 + row * 128);
@@ -737,10 +721,6 @@ decode_attn_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap map
     }
     ++segc;
   }
-  if (tid == 0) DEC_TRACE(3);
-#ifdef B200_TRACE
-  if (tid == 0) { g_dec_trace[blockIdx.x * 8 + 5] = segc; g_dec_trace[blockIdx.x * 8 + 6] = it; }
-#endif
   // tell the epilogue warp that nothing more will come
   if (ok) {
     const int e = segc % p.n_merge;
@@ -755,11 +735,6 @@ decode_attn_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap map
   }
 }
 
-#ifdef B200_TRACE
-extern "C" int b200_debug_trace(unsigned long long* host_out, int n) {
-  return static_cast<int>(cudaMemcpyFromSymbol(host_out, g_dec_trace, sizeof(unsigned long long) * n));
-}
-#endif
 
 int read_status_decode() {
   int v = 0;

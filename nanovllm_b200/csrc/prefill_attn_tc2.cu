@@ -38,21 +38,6 @@ constexpr float kT2Rescale = 8.0f;
 
 static __device__ int g_status_prefill_tc2 = 0;
 
-// Optional per-item timestamps of CTA 0..7 (compile with -DB200_TRACE; read with b200_debug_trace_prefill).
-#ifdef B200_TRACE
-constexpr int kT2TraceItems = 96, kT2TraceSlots = 12;
-__device__ unsigned long long g_pf_trace[8 * kT2TraceItems * kT2TraceSlots];
-__device__ __forceinline__ void pf_trace(int item, int slot, unsigned long long extra = 0) {
-  if (blockIdx.x < 8 && item < kT2TraceItems) {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    g_pf_trace[(blockIdx.x * kT2TraceItems + item) * kT2TraceSlots + slot] = extra ? extra : t;
-  }
-}
-#define PF_TRACE(...) pf_trace(__VA_ARGS__)
-#else
-#define PF_TRACE(...) do { } while (0)
-#endif
 static __device__ unsigned int g_prefill_ticket = 0;
 
 struct T2Item {
@@ -270,7 +255,6 @@ prefill_attn_tc2_kernel(const PrefillParams p, const __grid_constant__ CUtensorM
           s_item[is].k_begin = k_begin;
           s_item[is].n[0] = nA;
           s_item[is].n[1] = nB;
-          PF_TRACE(n_pub, 11, (static_cast<unsigned long long>(nA) << 8) | nB | (1ull << 32));
         }
         s_item[is].seq = seq;
         mbar_arrive(&bar_item_full[is]);                                // an item, or the end marker
@@ -283,7 +267,6 @@ prefill_attn_tc2_kernel(const PrefillParams p, const __grid_constant__ CUtensorM
           tma_prefetch_l2_3d(&map_q, 0, h * G, q_row + QT);
           tma_prefetch_l2_3d(&map_q, 64, h * G, q_row + QT);
         }
-        PF_TRACE(n_pub, 0);
         // Q tiles (the buffers are free once every S MMA of the previous item has completed)
         const uint32_t qph = (n_pub & 1) ^ 1;
         for (int hx = 0; hx < 2; ++hx) {
@@ -294,7 +277,6 @@ prefill_attn_tc2_kernel(const PrefillParams p, const __grid_constant__ CUtensorM
           tma_load_3d(sQ + hx * kT2Tile + kT2Sub, &map_q, &bar_q_full[hx], 64, h * G, q_row + hx * QT);
         }
         if (!ok) break;
-        PF_TRACE(n_pub, 1);
         ++n_pub;
         // K and V tiles
         const int* bt_row = p.block_tables ? p.block_tables + seq * p.bt_row_stride : nullptr;
@@ -351,19 +333,14 @@ prefill_attn_tc2_kernel(const PrefillParams p, const __grid_constant__ CUtensorM
           tc::mma_ts_lo(tmem + 256 + hx * 128, tmem + hx * 128 + ks * 8, v_lo + vslot * (kT2Tile >> 4) + ks * (2048 >> 4),
                         desc_hi, idesc_pv, accumulate || ks > 0);
       };
-#ifdef B200_TRACE
-      long long mk_of = 0;
-#endif
       while (ok) {
         const int is = n_item % kT2Items;
         if (!mbar_wait(&bar_item_full[is], (n_item / kT2Items) & 1, abort_flag)) break;
         const int seq = s_item[is].seq, nA = s_item[is].n[0], nB = s_item[is].n[1], n = max(nA, nB);
         mbar_arrive(&bar_item_empty[is]);
         if (seq < 0) break;
-        PF_TRACE(n_item, 2);
         const uint32_t qph = n_item & 1;
         if (!mbar_wait(&bar_q_full[0], qph, abort_flag) || !mbar_wait(&bar_q_full[1], qph, abort_flag)) break;
-        PF_TRACE(n_item, 3);
         // first K tile: S for both halves
         if (n > 0) {
           if (!mbar_wait(&bar_k_full[kt % kT2Ring], (kt / kT2Ring) & 1, abort_flag)) break;
@@ -372,7 +349,6 @@ prefill_attn_tc2_kernel(const PrefillParams p, const __grid_constant__ CUtensorM
           if (nB > 0) issue_s(1, kt % kT2Ring);
           tc::commit(&bar_k_empty[kt % kT2Ring]);
           ++kt;
-          PF_TRACE(n_item, 4);
         }
         if (nA <= 1) tc::commit(&bar_q_empty[0]);
         if (nB <= 1) tc::commit(&bar_q_empty[1]);
@@ -384,14 +360,8 @@ prefill_attn_tc2_kernel(const PrefillParams p, const __grid_constant__ CUtensorM
           if (j + 1 < n && !mbar_wait(&bar_k_full[kt % kT2Ring], (kt / kT2Ring) & 1, abort_flag)) { ok = false; break; }
           if (j == 0) {
             // the output warpgroup must have taken the previous item's O out of both accumulators
-#ifdef B200_TRACE
-            const long long tof = clock64();
-#endif
             if (nA > 0 && !mbar_wait(&bar_o_free[0], (no[0] & 1) ^ 1, abort_flag)) { ok = false; break; }
             if (nB > 0 && !mbar_wait(&bar_o_free[1], (no[1] & 1) ^ 1, abort_flag)) { ok = false; break; }
-#ifdef B200_TRACE
-            mk_of += clock64() - tof;
-#endif
           }
           for (int hx = 0; hx < 2 && ok; ++hx) {
             const int nx = hx == 0 ? nA : nB;
@@ -413,15 +383,8 @@ prefill_attn_tc2_kernel(const PrefillParams p, const __grid_constant__ CUtensorM
           ++vt;
           if (j + 1 < n) { tc::commit(&bar_k_empty[kt % kT2Ring]); ++kt; }
         }
-        PF_TRACE(n_item, 5);
         ++n_item;
       }
-#ifdef B200_TRACE
-      if (blockIdx.x < 8) {
-        unsigned long long* o = g_pf_trace + (blockIdx.x * kT2TraceItems + (kT2TraceItems - 2)) * kT2TraceSlots;
-        o[0] = n_item; o[1] = mk_of;
-      }
-#endif
     }
   }
   } else if (warp < 12) {
@@ -433,16 +396,10 @@ prefill_attn_tc2_kernel(const PrefillParams p, const __grid_constant__ CUtensorM
     const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
     const uint32_t tmem_s = tmem + hx * 128, tmem_o = tmem + 256 + hx * 128;
     const float c = p.scale_log2;
-    int n_item = 0, ns = 0, n_final = 0, vt_base = 0;
+    int n_item = 0, ns = 0, vt_base = 0;
     bool ok = true;
     int n_fin = 0;                                      // halves handed to the output warpgroup
 
-#ifdef B200_TRACE
-    long long ck_wait = 0, ck_ld = 0, ck_max = 0, ck_exp = 0, ck_sig = 0, ck_epi = 0, ck_tiles = 0, ck_t0 = 0;
-#define CK(var) do { const long long now_ = clock64(); var += now_ - ck_t0; ck_t0 = now_; } while (0)
-#else
-#define CK(var) do { } while (0)
-#endif
     while (ok) {
       const int is = n_item % kT2Items;
       if (!mbar_wait(&bar_item_full[is], (n_item / kT2Items) & 1, abort_flag)) break;
@@ -460,13 +417,8 @@ prefill_attn_tc2_kernel(const PrefillParams p, const __grid_constant__ CUtensorM
       const int first_row_kmax = shift + it.tq0 + hx * QT;
       float m_used = -INFINITY, l = 0.f;
       for (int j = 0; j < nx; ++j) {
-#ifdef B200_TRACE
-        ck_t0 = clock64(); ++ck_tiles;
-#endif
         if (!mbar_wait(&bar_s_full[hx], ns & 1, abort_flag)) { ok = false; break; }
-        CK(ck_wait);
         ++ns;
-        if (hx == 0 && r == 0 && j == 0) PF_TRACE(n_item - 1, 6);
         tc::fence_after_sync();
         const int key0 = j * kT2Kv;
         const bool need_mask = key0 + kT2Kv - 1 > first_row_kmax;
@@ -475,7 +427,6 @@ prefill_attn_tc2_kernel(const PrefillParams p, const __grid_constant__ CUtensorM
 #pragma unroll
         for (int cch = 0; cch < 4; ++cch) tc::ld_32x32b_x32(tmem_s + lane_base + cch * 32, sv[cch]);
         tc::wait_ld();
-        CK(ck_ld);
         if (need_mask) {
           const int nvalid = kmax - key0 + 1;           // columns of this row that may be seen
 #pragma unroll
@@ -524,7 +475,6 @@ prefill_attn_tc2_kernel(const PrefillParams p, const __grid_constant__ CUtensorM
             }
           }
         }
-        CK(ck_max);
         // P = exp2(c * (s - m)) (masked entries are -inf -> 0), row sum, packed bf16 back over S
         const float mc = (m_used == -INFINITY ? 0.f : m_used) * c;
         // packed 2 x fp32 FMA and ADD: half the instructions of the scalar form
@@ -560,7 +510,6 @@ prefill_attn_tc2_kernel(const PrefillParams p, const __grid_constant__ CUtensorM
           l0 = a0; l1 = a1; l2 = 0.f; l3 = 0.f;
         }
         l += (l0 + l1) + (l2 + l3);
-        CK(ck_exp);
         tc::wait_st();
         if (key0 + kT2Kv > it.Lk) {
           // ragged last tile of the sequence: V rows past its end are foreign data; zero them so
@@ -580,8 +529,6 @@ prefill_attn_tc2_kernel(const PrefillParams p, const __grid_constant__ CUtensorM
         tc::fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(&bar_p_full[hx]);   // one arrival per warp
-        CK(ck_sig);
-        if (hx == 0 && r == 0 && j == nx - 1) PF_TRACE(n_item - 1, 7);
       }
       if (!ok) break;
       vt_base += n_all;
@@ -599,12 +546,6 @@ prefill_attn_tc2_kernel(const PrefillParams p, const __grid_constant__ CUtensorM
         for (int i = 0; i < 16; ++i) dst[i] = make_uint4(0, 0, 0, 0);
       }
     }
-#ifdef B200_TRACE
-    if (hx == 0 && r == 0 && blockIdx.x < 8) {
-      unsigned long long* o = g_pf_trace + (blockIdx.x * kT2TraceItems + (kT2TraceItems - 1)) * kT2TraceSlots;
-      o[0] = ck_tiles; o[1] = ck_wait; o[2] = ck_ld; o[3] = ck_max; o[4] = ck_exp; o[5] = ck_sig; o[6] = ck_epi; o[7] = n_item;
-    }
-#endif
   } else {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 64;" ::: "memory");
     // ================================ output warpgroup ================================
@@ -614,16 +555,9 @@ prefill_attn_tc2_kernel(const PrefillParams p, const __grid_constant__ CUtensorM
     int n_item = 0;
     int nf[2] = {0, 0};                                  // halves drained so far
     bool ok = true;
-#ifdef B200_TRACE
-    long long ok_item = 0, ok_l = 0, ok_of = 0, ok_drain = 0, ok_n = 0, ok_t0 = clock64();
-#define OK(var) do { const long long now_ = clock64(); var += now_ - ok_t0; ok_t0 = now_; } while (0)
-#else
-#define OK(var) do { } while (0)
-#endif
     while (ok) {
       const int is = n_item % kT2Items;
       if (!mbar_wait(&bar_item_full[is], (n_item / kT2Items) & 1, abort_flag)) break;
-      OK(ok_item);
       const int seq = s_item[is].seq, h = s_item[is].h, q_row = s_item[is].q_row, tq0 = s_item[is].tq0, Lq = s_item[is].Lq;
       const int nA = s_item[is].n[0], nB = s_item[is].n[1];
       __syncwarp();
@@ -635,12 +569,10 @@ prefill_attn_tc2_kernel(const PrefillParams p, const __grid_constant__ CUtensorM
         if ((hx == 0 ? nA : nB) <= 0) continue;
         const uint32_t ph = nf[hx] & 1;
         if (!mbar_wait(&bar_l_full[hx], ph, abort_flag)) { ok = false; break; }
-        OK(ok_l);
         const float inv = s_inv[hx][r];
         __syncwarp();
         if (lane == 0) mbar_arrive(&bar_l_empty[hx]);
         if (!mbar_wait(&bar_o_final[hx], ph, abort_flag)) { ok = false; break; }
-        OK(ok_of);
         tc::fence_after_sync();
         const int tok_w = tq0 + hx * QT + (quarter * 32) / G;        // first token of this warp's rows
         if (p.out_tma && tok_w + 32 / G <= Lq) {
@@ -652,27 +584,12 @@ prefill_attn_tc2_kernel(const PrefillParams p, const __grid_constant__ CUtensorM
           t2_output(p, tmem + 256 + hx * 128 + lane_base, &bar_o_free[hx], sStage + quarter * 4096, lane, quarter, hx,
                     inv, q_row, h, tq0, Lq);
         }
-        OK(ok_drain);
-#ifdef B200_TRACE
-        ++ok_n;
-#endif
         ++nf[hx];
       }
     }
     if (lane == 0) tma_store_wait_read();                // the staging tile must outlive its last store
-#ifdef B200_TRACE
-    if (warp == 12 && lane == 0 && blockIdx.x < 8) {
-      unsigned long long* o = g_pf_trace + (blockIdx.x * kT2TraceItems + (kT2TraceItems - 3)) * kT2TraceSlots;
-      o[0] = ok_n; o[1] = ok_item; o[2] = ok_l; o[3] = ok_of; o[4] = ok_drain;
-    }
-#endif
   }
 
-#ifdef B200_TRACE
-  if (warp == 4 && lane == 0 && blockIdx.x < 8) {
-    // reuse the last trace rows of the CTA for the cycle breakdown of softmax warpgroup A, thread 0
-  }
-#endif
   // ---- teardown: everyone meets, then the allocating warp frees TMEM ----
   tc::fence_before_sync();
   __syncthreads();
@@ -683,11 +600,6 @@ prefill_attn_tc2_kernel(const PrefillParams p, const __grid_constant__ CUtensorM
   if (tid == 0 && s_abort) atomicExch(&g_status_prefill_tc2, 1);
 }
 
-#ifdef B200_TRACE
-extern "C" int b200_debug_trace_prefill(unsigned long long* host_out, int n) {
-  return static_cast<int>(cudaMemcpyFromSymbol(host_out, g_pf_trace, sizeof(unsigned long long) * n));
-}
-#endif
 
 int read_status_prefill_tc2() {
   int v = 0;
