@@ -108,13 +108,16 @@ def main():
     ap.add_argument("--out", default="")
     ap.add_argument("--fuse-producer", action="store_true",
                     help="with --attn ours: q_norm + k_norm + rotary_emb + cache store as one kernel")
+    ap.add_argument("--small-allreduce", action="store_true",
+                    help="with --attn ours: also the one-shot all-reduce for decode-sized messages (implies --fast-metadata)")
     ap.add_argument("--fast-metadata", action="store_true",
                     help="with --attn ours: also the packed one-copy / one-launch decode metadata preparation "
                          "(implies --fuse-producer)")
     args = ap.parse_args()
-    want_fast = args.fast_metadata and args.attn == "ours"
+    want_ar = args.small_allreduce and args.attn == "ours"
+    want_fast = (args.fast_metadata or want_ar) and args.attn == "ours"
     want_fuse = "1" if ((args.fuse_producer or want_fast) and args.attn == "ours") else "0"
-    want_env = "" if args.attn == "reference" else ("full" if want_fast else ("fused" if want_fuse == "1" else "1"))
+    want_env = "" if args.attn == "reference" else ("full+ar" if want_ar else ("full" if want_fast else ("fused" if want_fuse == "1" else "1")))
     if os.environ.get("B200_ATTN_INSTALL", "") != want_env:
         # set before anything of the engine is imported (and for spawned ranks), then start over
         os.environ["B200_ATTN_INSTALL"] = want_env
@@ -147,7 +150,7 @@ def main():
     produced = sum(len(o["token_ids"]) for o in outs)
     res = {
         "metric": "e2e_output_tok_per_s", "value": round(total / t, 2), "unit": "tok/s", "attn": args.attn,
-        "fused_producer": want_fuse == "1", "fast_decode_metadata": bool(want_fast),
+        "fused_producer": want_fuse == "1", "fast_decode_metadata": bool(want_fast), "small_allreduce": bool(want_ar),
         "attention_module": attn_mod.__name__ + " from " + os.path.relpath(attn_mod.__file__, ROOT),
         "tp": args.tp, "num_seqs": args.num_seqs, "output_tokens": total, "produced_tokens": produced,
         "input_tokens": sum(len(p) for p in prompts), "seconds": round(t, 3), "engine_init_s": round(t_init, 1),

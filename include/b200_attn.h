@@ -167,6 +167,33 @@ int b200_unpack_decode_metadata(const void* packed, int32_t batch, int32_t table
                                 int32_t buffer_table_cols, int64_t* input_ids, int64_t* positions,
                                 int32_t* slot_mapping, int32_t* context_lens, int32_t* block_tables, void* stream);
 
+/* ---- behind the path: the all-reduce after the output projection, for decode-sized messages ---------------
+ * Replaces `dist.all_reduce(y)` in RowParallelLinear.forward (nanovllm/layers/linear.py:149-153) when y is at
+ * most b200_small_allreduce_max_bytes() (512 KiB) of bf16: a one-shot sum over plain peer loads and stores.
+ * Set-up is the caller's: every rank allocates an exchange buffer of b200_small_allreduce_buffer_bytes(),
+ * zero-filled, shares it with the other ranks of the node (CUDA IPC) and passes the `world` device pointers under
+ * which IT sees the ranks' buffers (own buffer at index `rank`; a HOST array of pointers), plus a private,
+ * zero-filled device block of b200_small_allreduce_state_bytes().  All ranks must make the same sequence of calls
+ * with the same sizes.  inout (n_elems bf16, a multiple of 8, 16-byte aligned) is replaced by the sum over ranks,
+ * accumulated in fp32 in rank order (every rank gets identical bits).  Every wait is bounded
+ * (wait_limit_seconds, default 1 s when <= 0): a rank whose peers do not show up leaves its message unchanged
+ * and sets a status word, read with b200_small_allreduce_status(); after that the ranks must zero their buffers
+ * and state blocks together before the next call.  The launch can be captured in a CUDA graph. */
+int64_t b200_small_allreduce_buffer_bytes(void);
+int64_t b200_small_allreduce_state_bytes(void);
+int64_t b200_small_allreduce_max_bytes(void);
+int b200_small_allreduce(void* const* peer_buffers, int32_t rank, int32_t world, void* local_state, void* inout,
+                         int64_t n_elems, double wait_limit_seconds, void* stream);
+/* Synchronises the current device and returns B200_ERR_TIMEOUT if a wait of b200_small_allreduce gave up since the
+ * state block was zero-filled, else 0. */
+int b200_small_allreduce_status(const void* local_state);
+/* Set-up helpers for the exchange buffers (no counterpart in the reference, which leaves this to NCCL): export a
+ * device buffer of this process as a 64-byte CUDA IPC handle plus the buffer's offset inside its allocation, and map
+ * a buffer exported by another process into the current device's address space.  The mapping lasts until the process
+ * exits.  Host pointers for handle, offset and result. */
+int b200_ipc_export(const void* ptr, void* handle_out_64_bytes, int64_t* offset_out);
+int b200_ipc_open(const void* handle_64_bytes, int64_t offset, void** ptr_out);
+
 /* Number of kernels this library has launched from the calling process so far (all threads).
  * Benchmarks use the difference across a timed region. */
 int64_t b200_launch_count(void);

@@ -7,7 +7,7 @@ from __future__ import annotations
 
 import ctypes
 import os
-from ctypes import c_char_p, c_float, c_int32, c_int64, c_void_p
+from ctypes import c_char_p, c_double, c_float, c_int32, c_int64, c_void_p
 
 from .build import LIB_PATH, build
 
@@ -36,6 +36,13 @@ SIGNATURES = {
                                           c_int32, c_int32, c_void_p]),
     "b200_unpack_decode_metadata": (c_int32, [c_void_p, c_int32, c_int32, c_int32, c_int32, c_void_p, c_void_p, c_void_p,
                                               c_void_p, c_void_p, c_void_p]),
+    "b200_small_allreduce_buffer_bytes": (c_int64, []),
+    "b200_small_allreduce_state_bytes": (c_int64, []),
+    "b200_small_allreduce_max_bytes": (c_int64, []),
+    "b200_small_allreduce": (c_int32, [c_void_p, c_int32, c_int32, c_void_p, c_void_p, c_int64, c_double, c_void_p]),
+    "b200_small_allreduce_status": (c_int32, [c_void_p]),
+    "b200_ipc_export": (c_int32, [c_void_p, c_void_p, c_void_p]),
+    "b200_ipc_open": (c_int32, [c_void_p, c_int64, c_void_p]),
     "b200_launch_count": (c_int64, []),
     "b200_device_status": (c_int32, []),
     "b200_test_inject_timeout": (c_int32, []),

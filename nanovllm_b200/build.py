@@ -16,7 +16,7 @@ import sys
 PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG_DIR, "csrc")
 LIB_PATH = os.path.join(PKG_DIR, "libb200attn.so")
-SOURCES = ["host.cu", "store_kvcache.cu", "decode_attn.cu", "prefill_attn_mma.cu", "prefill_attn_tc2.cu", "prefill_attn.cu", "qk_norm_rope_store.cu", "decode_metadata.cu"]
+SOURCES = ["host.cu", "store_kvcache.cu", "decode_attn.cu", "prefill_attn_mma.cu", "prefill_attn_tc2.cu", "prefill_attn.cu", "qk_norm_rope_store.cu", "decode_metadata.cu", "small_allreduce.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-shared", "-Xcompiler", "-fPIC"]
 

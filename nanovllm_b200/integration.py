@@ -18,13 +18,15 @@ import importlib
 import sys
 
 
-def install(fuse_qk_norm_rope: bool = False, fast_decode_metadata: bool = False):
+def install(fuse_qk_norm_rope: bool = False, fast_decode_metadata: bool = False, small_allreduce: bool = False):
     """fuse_qk_norm_rope=True additionally replaces the body of `Qwen3Attention.forward`
     (nanovllm/models/qwen3.py:68-82) by one that runs q_norm, k_norm, rotary_emb and the cache store as a
     single kernel (layers/qk_norm_rope.py); nano-vllm's model module is imported for that.
     fast_decode_metadata=True rebinds `ModelRunner.prepare_decode` and the graph branch of `ModelRunner.run_model`
     (nanovllm/engine/model_runner.py:163-179, :188-205) to the packed one-copy, one-launch form of
-    engine/decode_metadata.py."""
+    engine/decode_metadata.py.
+    small_allreduce=True rebinds `RowParallelLinear.forward` (nanovllm/layers/linear.py:149-153) so that bf16 messages
+    of at most 512 KiB are summed by the one-shot peer-memory kernel of engine/small_allreduce.py instead of NCCL."""
     from .layers import attention as ours
     ref_attn = sys.modules.get("nanovllm.layers.attention")
     if ref_attn is None:
@@ -50,4 +52,7 @@ def install(fuse_qk_norm_rope: bool = False, fast_decode_metadata: bool = False)
         from .engine.decode_metadata import install_into
         runner = importlib.import_module("nanovllm.engine.model_runner")
         install_into(runner.ModelRunner, ref_ctx)
+    if small_allreduce:
+        from .engine.small_allreduce import install_into as install_allreduce
+        install_allreduce(importlib.import_module("nanovllm.layers.linear"))
     return ours
