@@ -161,6 +161,9 @@ def main():
         from nanovllm_b200 import _lib
         res["lib_launches_rank0_eager"] = int(_lib.load().b200_launch_count() - lib_launches0)
         _lib.check(_lib.load().b200_device_status())
+        if want_ar:
+            from nanovllm_b200.engine.small_allreduce import SmallAllReduce
+            res["small_allreduce_rank0"] = [{"status": c.status(), "host_calls": c.calls} for c in SmallAllReduce.instances]
     line = json.dumps(res)
     print(line, flush=True)
     if args.out:

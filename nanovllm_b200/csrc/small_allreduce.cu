@@ -1,23 +1,24 @@
 // One-shot all-reduce (sum) of a small bf16 message across the tensor-parallel ranks of one node,
-// over plain peer loads and stores (CUDA IPC mappings of every rank's exchange buffer; no multimem,
-// no TMA, no library kernel on peer memory).  Replaces, for decode-sized messages, the NCCL call
-// after the row-parallel output projection (nanovllm/layers/linear.py:149-153, `dist.all_reduce(y)`):
-// 56 of them per decode step of a 28-layer model, each at most batch x hidden x 2 bytes (512 KiB at
-// batch 256, hidden 1024), where a ring or tree collective is pure latency.
+// over plain peer stores (CUDA IPC mappings of every rank's exchange buffer; no multimem, no TMA, no
+// library kernel on peer memory).  Replaces, for decode-sized messages, the NCCL call after the
+// row-parallel output projection (nanovllm/layers/linear.py:149-153, `dist.all_reduce(y)`): 56 of them
+// per decode step of a 28-layer model, each at most batch x hidden x 2 bytes (512 KiB at batch 256,
+// hidden 1024), where a collective is pure latency.
 //
-// Every rank owns an exchange buffer that all ranks have mapped:
-//   data   two slots of kArMaxBytes (calls alternate, so a rank that is already in the next call never
-//          overwrites what a slower rank is still reading)
-//   flags  [kArMaxCtas][kArMaxRanks] epoch words, written by the peers, polled locally
-// CTA c of every rank handles slice c of the message, and only ever waits for CTA c of the other
-// ranks: (A) copy the slice of the input into the own data slot, (B) store the call's epoch into the
-// flag word (c, own rank) of EVERY rank (release at system scope after a CTA barrier), (C) wait until
-// the own flag words (c, r) of all ranks r have reached the epoch (acquire loads of LOCAL memory;
-// bounded: after the limit the CTA records a status and leaves its slice unwritten), (D) load the
-// slice from every rank's slot and add in fp32 in rank order -- the same order on every rank, so all
-// ranks end up with identical bits -- and write bf16 back in place.
-// The epoch of a CTA index lives in local device memory and is advanced by the kernel itself, so a
-// captured launch can be replayed; all ranks must issue the same sequence of calls (same sizes).
+// Push, with the flag travelling inside the data: every rank owns an exchange buffer that all ranks
+// have mapped, laid out [2 slots][source rank][message as 16-byte words].  A sender writes each 8 bytes
+// of its message (4 bf16) as one 16-byte word {data, epoch, data, epoch} straight into the region that
+// is its own in every peer's buffer; a receiver polls its LOCAL buffer word by word until both epoch
+// fields of a word equal the call's epoch, and adds the ranks' values in fp32 in rank order (the same
+// order everywhere: all ranks end up with identical bits).  No fence, no barrier, no read over NVLink:
+// the latency of a call is one posted store across the link plus a local poll.  Calls alternate
+// between the two slots, so a rank that is already in the next call never overwrites words a slower
+// rank is still waiting for (to get two calls ahead it would need that rank's data of the call in
+// between).  The epoch is one word of local device memory, read by every CTA on entry and advanced by
+// the last CTA to leave, so a captured launch can be replayed; it is unique per call, which is what
+// makes a stale word from any earlier call (of whatever size) impossible to mistake for a fresh one.
+// All ranks must issue the same sequence of calls.  Every poll is bounded: after the limit the thread
+// records a status and leaves its part of the message unchanged.
 #include <cstring>
 
 #include "../../include/b200_attn.h"
@@ -27,30 +28,25 @@ namespace b200 {
 extern std::atomic<long long> g_launches;
 
 constexpr int kArMaxRanks = 8;
-constexpr int kArMaxCtas = 64;
+constexpr int kArMaxCtas = 32;
 constexpr int kArThreads = 512;
-constexpr long long kArMaxBytes = 512 * 1024;           // per message
-constexpr long long kArDataBytes = 2 * kArMaxBytes;     // two slots
-constexpr long long kArFlagBytes = kArMaxCtas * kArMaxRanks * 4;
+constexpr long long kArMaxBytes = 512 * 1024;                       // per message
+constexpr long long kArRegionBytes = 2 * kArMaxBytes;               // a message as flagged 16-byte words
+constexpr long long kArSlotBytes = kArMaxRanks * kArRegionBytes;    // one region per source rank
+constexpr long long kArBufferBytes = 2 * kArSlotBytes;              // two slots
+constexpr int kArStateWords = 4;                                    // epoch, CTAs done, status, pad
 
 struct ArParams {
   unsigned char* peer[kArMaxRanks];     // every rank's exchange buffer as mapped here (own included)
-  unsigned int* epochs;                 // [kArMaxCtas] local
-  int* status;                          // local: set to 1 if a wait gave up
+  unsigned int* state;                  // local: [0] epoch of the last finished call, [1] CTAs done, [2] status
   __nv_bfloat16* inout;
-  long long n_elems;
-  long long chunk_elems;                // per CTA, a multiple of 8
+  long long n_words;                    // 8-byte payload words (4 bf16 each)
   long long spin_limit;                 // cycles
   int rank, world;
 };
 
-__device__ __forceinline__ void st_release_sys(unsigned int* p, unsigned int v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
-  unsigned int v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
+__device__ __forceinline__ void st_volatile_v4(void* p, uint4 v) {
+  asm volatile("st.volatile.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
 __device__ __forceinline__ uint4 ld_volatile_v4(const void* p) {
   uint4 v;
@@ -61,88 +57,77 @@ __device__ __forceinline__ uint4 ld_volatile_v4(const void* p) {
 __global__ void __launch_bounds__(kArThreads)
 small_allreduce_kernel(const ArParams p) {
   __shared__ unsigned int s_epoch;
-  __shared__ int s_fail;
-  const int c = blockIdx.x, tid = threadIdx.x;
-  if (tid == 0) {
-    s_epoch = p.epochs[c] + 1;
-    s_fail = 0;
-  }
+  const int tid = threadIdx.x;
+  if (tid == 0) s_epoch = *reinterpret_cast<volatile unsigned int*>(p.state) + 1;
   __syncthreads();
   const unsigned int e = s_epoch;
-  const long long slot_off = static_cast<long long>(e & 1u) * kArMaxBytes;
-  const long long begin = static_cast<long long>(c) * p.chunk_elems;
-  long long end = begin + p.chunk_elems;
-  if (end > p.n_elems) end = p.n_elems;
-  const long long nvec = begin < end ? (end - begin + 7) / 8 : 0;      // 16-byte vectors (n_elems is a multiple of 8)
-  // (A) the slice of the input into this rank's slot
-  {
-    const uint4* src = reinterpret_cast<const uint4*>(p.inout + begin);
-    uint4* dst = reinterpret_cast<uint4*>(p.peer[p.rank] + slot_off + begin * 2);
-    for (long long v = tid; v < nvec; v += kArThreads) dst[v] = src[v];
-  }
-  __syncthreads();
-  // (B) tell every rank (this one included) that slice c of this rank is in place
-  if (tid < p.world) {
-    __threadfence_system();
-    unsigned int* flags = reinterpret_cast<unsigned int*>(p.peer[tid] + kArDataBytes);
-    st_release_sys(flags + c * kArMaxRanks + p.rank, e);
-  }
-  // (C) wait for slice c of every rank
-  if (tid < p.world) {
-    const unsigned int* mine = reinterpret_cast<const unsigned int*>(p.peer[p.rank] + kArDataBytes) + c * kArMaxRanks + tid;
-    const long long t0 = clock64();
-    int spins = 0;
-    // epochs only grow; a peer may already have signalled the next call
-    while (static_cast<int>(ld_acquire_sys(mine) - e) < 0) {
-      if ((++spins & 63) == 0 && clock64() - t0 > p.spin_limit) {
-        s_fail = 1;
-        break;
-      }
-    }
-  }
-  __syncthreads();
-  if (s_fail) {
-    if (tid == 0) {
-      atomicExch(p.status, 1);
-      p.epochs[c] = e;
-    }
-    return;
-  }
-  // (D) sum in rank order, fp32, one rounding
-  uint4* out = reinterpret_cast<uint4*>(p.inout + begin);
-  for (long long v = tid; v < nvec; v += kArThreads) {
-    float acc[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-    uint4 raw[kArMaxRanks];
+  const long long slot_off = static_cast<long long>(e & 1u) * kArSlotBytes;
+  const long long stride = static_cast<long long>(gridDim.x) * kArThreads;
+  const long long first = static_cast<long long>(blockIdx.x) * kArThreads + tid;
+  const uint2* in = reinterpret_cast<const uint2*>(p.inout);
+  // push: this rank's words into its region of every peer's buffer
+  for (long long w = first; w < p.n_words; w += stride) {
+    const uint2 x = in[w];
+    const uint4 flagged = make_uint4(x.x, e, x.y, e);
 #pragma unroll
     for (int r = 0; r < kArMaxRanks; ++r)
-      if (r < p.world) raw[r] = ld_volatile_v4(p.peer[r] + slot_off + begin * 2 + v * 16);
+      if (r < p.world && r != p.rank)
+        st_volatile_v4(p.peer[r] + slot_off + static_cast<long long>(p.rank) * kArRegionBytes + w * 16, flagged);
+  }
+  // gather: the peers' words as they land in the local buffer, summed in rank order
+  const unsigned char* mine = p.peer[p.rank] + slot_off;
+  bool failed = false;
+  const long long t0 = clock64();
+  uint2* out = reinterpret_cast<uint2*>(p.inout);
+  for (long long w = first; w < p.n_words && !failed; w += stride) {
+    const uint2 own = in[w];
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
     for (int r = 0; r < kArMaxRanks; ++r) {
-      if (r < p.world) {
-        const uint32_t w[4] = {raw[r].x, raw[r].y, raw[r].z, raw[r].w};
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          acc[2 * i] += __uint_as_float(w[i] << 16);
-          acc[2 * i + 1] += __uint_as_float(w[i] & 0xffff0000u);
+      if (r >= p.world) break;
+      uint32_t lo, hi;
+      if (r == p.rank) {
+        lo = own.x;
+        hi = own.y;
+      } else {
+        const unsigned char* src = mine + static_cast<long long>(r) * kArRegionBytes + w * 16;
+        uint4 v = ld_volatile_v4(src);
+        int spins = 0;
+        while (v.y != e || v.w != e) {
+          if ((++spins & 63) == 0 && clock64() - t0 > p.spin_limit) {
+            failed = true;
+            break;
+          }
+          v = ld_volatile_v4(src);
         }
+        lo = v.x;
+        hi = v.z;
       }
+      acc[0] += __uint_as_float(lo << 16);
+      acc[1] += __uint_as_float(lo & 0xffff0000u);
+      acc[2] += __uint_as_float(hi << 16);
+      acc[3] += __uint_as_float(hi & 0xffff0000u);
     }
-    uint4 o;
-    o.x = pack_bf16(acc[0], acc[1]);
-    o.y = pack_bf16(acc[2], acc[3]);
-    o.z = pack_bf16(acc[4], acc[5]);
-    o.w = pack_bf16(acc[6], acc[7]);
-    out[v] = o;
+    if (!failed) out[w] = make_uint2(pack_bf16(acc[0], acc[1]), pack_bf16(acc[2], acc[3]));
   }
-  if (tid == 0) p.epochs[c] = e;
+  if (failed) atomicExch(p.state + 2, 1u);
+  // the last CTA to leave advances the epoch (every CTA has read it by then)
+  __syncthreads();
+  if (tid == 0) {
+    __threadfence();
+    const unsigned int done = atomicAdd(p.state + 1, 1u);
+    if (done == gridDim.x - 1) {
+      p.state[1] = 0;
+      __threadfence();
+      *reinterpret_cast<volatile unsigned int*>(p.state) = e;
+    }
+  }
 }
 
 }  // namespace b200
 
-extern "C" int64_t b200_small_allreduce_buffer_bytes(void) { return b200::kArDataBytes + b200::kArFlagBytes; }
-extern "C" int64_t b200_small_allreduce_state_bytes(void) { return b200::kArMaxCtas * 4 + 64; }
+extern "C" int64_t b200_small_allreduce_buffer_bytes(void) { return b200::kArBufferBytes; }
+extern "C" int64_t b200_small_allreduce_state_bytes(void) { return b200::kArStateWords * 4; }
 extern "C" int64_t b200_small_allreduce_max_bytes(void) { return b200::kArMaxBytes; }
 
 extern "C" int b200_small_allreduce(void* const* peer_buffers, int32_t rank, int32_t world, void* local_state,
@@ -163,19 +148,14 @@ extern "C" int b200_small_allreduce(void* const* peer_buffers, int32_t rank, int
     if (r < world && (!p.peer[r] || (reinterpret_cast<uintptr_t>(p.peer[r]) & 15)))
       return set_error(kErrNullPointer, "small_allreduce: exchange buffer of rank %d missing or misaligned", r);
   }
-  p.epochs = static_cast<unsigned int*>(local_state);
-  p.status = reinterpret_cast<int*>(static_cast<unsigned char*>(local_state) + kArMaxCtas * 4);
+  p.state = static_cast<unsigned int*>(local_state);
   p.inout = static_cast<__nv_bfloat16*>(inout);
-  p.n_elems = n_elems;
+  p.n_words = n_elems / 4;
   p.rank = rank;
   p.world = world;
-  // 16 KiB of the message per CTA, at most kArMaxCtas of them; the same on every rank for the same size
-  long long ctas = (n_elems * 2 + 16383) / 16384;
+  // 8 KiB of the message per CTA, at most kArMaxCtas of them; the same on every rank for the same size
+  long long ctas = (n_elems * 2 + 8191) / 8192;
   if (ctas > kArMaxCtas) ctas = kArMaxCtas;
-  long long chunk = (n_elems + ctas - 1) / ctas;
-  chunk = (chunk + 7) / 8 * 8;
-  p.chunk_elems = chunk;
-  ctas = (n_elems + chunk - 1) / chunk;
   if (wait_limit_seconds <= 0.0 || wait_limit_seconds > 10.0) wait_limit_seconds = 1.0;
   p.spin_limit = static_cast<long long>(wait_limit_seconds * 2.0e9);
   small_allreduce_kernel<<<static_cast<unsigned>(ctas), kArThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
@@ -189,7 +169,7 @@ extern "C" int b200_small_allreduce_status(const void* local_state) {
   if (cudaDeviceSynchronize() != cudaSuccess)
     return check_cuda(cudaGetLastError(), "small_allreduce_status: cudaDeviceSynchronize");
   int v = 0;
-  const int rc = check_cuda(cudaMemcpy(&v, static_cast<const unsigned char*>(local_state) + kArMaxCtas * 4, sizeof(int),
+  const int rc = check_cuda(cudaMemcpy(&v, static_cast<const unsigned char*>(local_state) + 8, sizeof(int),
                                        cudaMemcpyDeviceToHost),
                             "small_allreduce_status: reading the status word");
   if (rc) return rc;

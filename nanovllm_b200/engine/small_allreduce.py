@@ -22,6 +22,8 @@ from .. import _lib
 
 
 class SmallAllReduce:
+    instances: list = []       # every communicator of this process (diagnostics: their status after a run)
+
     def __init__(self, group=None, wait_limit_seconds: float = 1.0):
         """Collective: every rank of `group` (default: the world) must construct it at the same point.
         All ranks must be processes on one node, one GPU each, current device already set."""
@@ -52,6 +54,8 @@ class SmallAllReduce:
             ptrs[r] = out.value
         self._ptrs = ptrs          # host array handed to every call (the library copies it into the launch)
         dist.barrier(group=group)  # nobody signals into a buffer that is not mapped and zeroed yet
+        self.calls = 0
+        SmallAllReduce.instances.append(self)
 
     def usable(self, t: torch.Tensor) -> bool:
         return (t.is_cuda and t.dtype == torch.bfloat16 and t.is_contiguous() and t.numel() % 8 == 0
@@ -61,6 +65,7 @@ class SmallAllReduce:
         """In place: t <- sum over ranks (fp32 accumulation in rank order, one rounding to bf16)."""
         _lib.check(self.lib.b200_small_allreduce(self._ptrs, self.rank, self.world, self.state.data_ptr(), t.data_ptr(),
                                                  t.numel(), self.wait_limit, torch.cuda.current_stream().cuda_stream))
+        self.calls += 1
         return t
 
     def status(self) -> int:
