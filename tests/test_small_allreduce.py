@@ -92,12 +92,14 @@ def _child(rank, world, port, out_dir):
 
 
 @pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs two GPUs on one node")
-def test_small_allreduce_two_ranks(tmp_path):
+def test_small_allreduce_ranks(tmp_path):
+    """Two ranks, or B200_AR_TEST_WORLD of them (up to 8) where that many GPUs are visible."""
+    world = min(int(os.environ.get("B200_AR_TEST_WORLD", "2")), torch.cuda.device_count(), 8)
     s = socket.socket()
     s.bind(("127.0.0.1", 0))
     port = s.getsockname()[1]
     s.close()
-    mp.spawn(_child, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    mp.spawn(_child, args=(world, port, str(tmp_path)), nprocs=world, join=True)
     assert "timeout and recovery ok" in open(os.path.join(str(tmp_path), "ok.txt")).read()
 
 
