@@ -46,7 +46,8 @@ def _child(rank, world, port, out_dir):
             got = comm.all_reduce_(x.clone())
             torch.cuda.synchronize()
             assert torch.equal(got, want), (n, it)
-            torch.testing.assert_close(got.float(), nccl.float(), atol=2e-2, rtol=1e-2)
+            # NCCL adds in bf16, in an order of its own: up to one bf16 rounding (2^-8 relative) per rank apart
+            torch.testing.assert_close(got.float(), nccl.float(), atol=2e-2, rtol=2.0 ** -8 * world)
     log.append("eager ok")
     # the shape the engine sends: (batch, hidden) rows, inside a captured graph, replayed with fresh data
     static = torch.zeros(64, 1024, device=dev, dtype=torch.bfloat16)
