@@ -93,7 +93,8 @@ def install_into(linear_module):
         y = F.linear(x, self.weight, self.bias if self.tp_rank == 0 else None)
         if self.tp_size > 1:
             comm = holder["comm"]
-            small = y.dtype == torch.bfloat16 and y.is_contiguous() and 0 < y.numel() * 2 <= 512 * 1024 and y.numel() % 8 == 0
+            small = (y.is_cuda and y.dtype == torch.bfloat16 and y.is_contiguous() and 0 < y.numel() * 2 <= 512 * 1024
+                     and y.numel() % 8 == 0)
             if small and comm is None and not torch.cuda.is_current_stream_capturing():
                 comm = holder["comm"] = SmallAllReduce()
             if small and comm is not None and comm.usable(y):

@@ -130,3 +130,41 @@ print(auto.installed, sys.modules.get('nanovllm.layers.attention') is ours)
     res = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, env=env)
     assert res.returncode == 0, res.stdout + res.stderr
     assert res.stdout.split() == [str(expect), str(expect)]
+
+
+def _row_parallel_rank(rank, world, port, out_dir):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, REF)
+    import nanovllm.layers.linear as linear
+    from nanovllm_b200.engine.small_allreduce import install_into
+    g = torch.Generator().manual_seed(3)
+    w = torch.randn(16, 8 * world, generator=g)
+    x = torch.randn(5, 8 * world, generator=g)
+    layer = linear.RowParallelLinear(8 * world, 16)
+    layer.weight.data.copy_(w[:, rank * 8:(rank + 1) * 8])
+    want = layer(x[:, rank * 8:(rank + 1) * 8])             # the reference's forward: F.linear + dist.all_reduce
+    install_into(linear)
+    got = layer(x[:, rank * 8:(rank + 1) * 8])              # rebound forward; CPU tensors take the same collective
+    ok = torch.equal(got, want) and torch.allclose(got, x @ w.t(), atol=1e-5)
+    flags = [None] * world
+    dist.all_gather_object(flags, ok)
+    if rank == 0:
+        torch.save({"ok": all(flags)}, os.path.join(out_dir, "rp.pt"))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.skipif(not os.path.isdir(os.path.join(REF, "nanovllm")), reason="reference install (baseline/_ref) not present")
+def test_row_parallel_forward_hook_keeps_the_collective_for_other_tensors(tmp_path):
+    """The rebound RowParallelLinear.forward (small bf16 CUDA messages go to the one-shot kernel) must leave every
+    other tensor on `dist.all_reduce`: two gloo ranks on the CPU, result equal to the reference's own forward."""
+    import socket
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    mp.spawn(_row_parallel_rank, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    assert torch.load(os.path.join(str(tmp_path), "rp.pt"))["ok"]
