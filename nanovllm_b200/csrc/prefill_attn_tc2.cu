@@ -3,7 +3,8 @@
 // and for K/V read from the paged cache.
 //
 // One persistent CTA per SM.  A work item is (sequence, kv head, block of 2 * QT query tokens),
-// QT = 128 / G, handed out through an atomic ticket counter, heaviest query blocks first.  The two
+// QT = 128 / G, handed out through an atomic ticket counter in reverse slot order (the last sequence first, and
+// within a sequence its last, longest query block first; not sorted by work across sequences).  The two
 // halves of the block ("A" = first QT tokens, "B" = next QT) are two independent 128-row tiles that
 // share every K/V tile, so K/V traffic per query row is halved and, more to the point, the tensor
 // core always has the other half's MMA to run while one half is in its softmax:
@@ -226,7 +227,7 @@ prefill_attn_tc2_kernel(const PrefillParams p, const __grid_constant__ CUtensorM
         bool b_rows = false;                                            // half B holds query rows
         if (tk < n_items) {
           h = tk % p.Hkv;
-          const int x = p.n_slots - 1 - static_cast<int>(tk / p.Hkv);   // later (heavier) blocks first
+          const int x = p.n_slots - 1 - static_cast<int>(tk / p.Hkv);   // reverse slot order: within a sequence the later, longer blocks come first
           int lo = 0, hi = p.batch;
           while (hi - lo > 1) {
             const int mid = (lo + hi) >> 1;
