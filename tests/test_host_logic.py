@@ -168,3 +168,20 @@ def test_row_parallel_forward_hook_keeps_the_collective_for_other_tensors(tmp_pa
     s.close()
     mp.spawn(_row_parallel_rank, args=(2, port, str(tmp_path)), nprocs=2, join=True)
     assert torch.load(os.path.join(str(tmp_path), "rp.pt"))["ok"]
+
+
+def test_packed_buffers_layout_and_views():
+    """engine.packed_copy: several tensors as one record, views with the requested shapes and dtypes, 16-byte aligned."""
+    from nanovllm_b200.engine.packed_copy import PackedBuffers
+    spec = {"q": ((3, 2, 128), torch.bfloat16), "slots": ((3,), torch.int32), "ids": ((3,), torch.int64),
+            "bt": ((3, 5), torch.int32)}
+    pb = PackedBuffers(spec, "cpu")
+    assert pb.nbytes % 16 == 0 and pb.nbytes >= 3 * 2 * 128 * 2 + 12 + 24 + 60
+    for name, (shape, dtype) in spec.items():
+        assert tuple(pb.host[name].shape) == shape and pb.host[name].dtype == dtype
+        assert pb.host[name].data_ptr() % 16 == 0
+    pb.host["ids"].copy_(torch.tensor([7, 8, 9]))
+    pb.host["bt"].fill_(-1)
+    dev = pb.upload()
+    assert torch.equal(dev["ids"], torch.tensor([7, 8, 9])) and bool((dev["bt"] == -1).all())
+    assert not dev["slots"].data_ptr() == pb.host["slots"].data_ptr()
