@@ -6,9 +6,10 @@
  *
  * Conventions
  *  - Every pointer is a device pointer on the current CUDA device unless stated otherwise.
- *    The library never allocates, frees or copies device memory and never synchronises; every
- *    launch goes to `stream` (a cudaStream_t passed as void*; NULL = legacy default stream), so
- *    calls can be captured into CUDA graphs.
+ *    The compute entry points never allocate, free or copy device memory and never synchronise;
+ *    every launch goes to `stream` (a cudaStream_t passed as void*; NULL = legacy default stream),
+ *    so calls can be captured into CUDA graphs.  The exceptions say so in their own comments: the
+ *    two status queries synchronise the device, b200_ipc_open maps another process's buffer.
  *  - Activations and caches are bf16 for the attention entry points.  head_dim must be 128.
  *  - Strides are in ELEMENTS.  Pointers and row strides must be 16-byte aligned.
  *  - The paged cache has the reference's layout (nanovllm/engine/model_runner.py:107-117): one
