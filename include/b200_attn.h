@@ -75,7 +75,11 @@ int64_t b200_decode_workspace_bytes(int32_t max_batch, int32_t num_heads, int32_
  * h to kv head h / (num_heads / num_kv_heads); softmax(scale * q k^T) v with fp32 softmax and
  * accumulation; out[i] (num_heads x head_dim, contiguous rows of num_heads * head_dim) in bf16.
  * context_lens[i] <= 0 writes zeros and touches no cache.  The launch geometry depends only on
- * (batch, head geometry), never on device data. */
+ * (batch, head geometry), never on device data.  The launch may begin while the previous kernel of
+ * the stream is still running if that kernel lets it (programmatic dependent launch: of this library
+ * b200_store_kvcache and b200_qk_norm_rope_store do); it reads context_lens and block_tables before it
+ * waits for that kernel, so a kernel that triggers its dependents early must not be the writer of
+ * those two arrays. */
 int b200_decode_attn(const void* q, int64_t q_row_stride, const void* k_cache, const void* v_cache,
                      int64_t num_blocks, int32_t block_size, const int32_t* block_tables, int64_t bt_row_stride,
                      int32_t bt_cols, const int32_t* context_lens, void* out, void* workspace,
